@@ -1,0 +1,357 @@
+// C ABI of the sm_100a backend: tensor-map construction, kernel selection and
+// launch.  Everything here enqueues work on the caller's stream and returns;
+// no device memory is allocated or freed.
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/fuseml_sm100.h"
+#include "aux_kernels.cuh"
+#include "gemm_kernel.cuh"
+#include "host_plan.h"
+
+namespace fuseml {
+
+// Status word written by bounded waits that ran out (0 = none did).
+__device__ int32_t g_status_word = 0;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+// 2-D row-major view [rows, cols] with `ld` elements between rows; box = {box_cols, box_rows},
+// 128-byte swizzle (box_cols * element size == 128).
+static int encode_2d(CUtensorMap* tm, int32_t dtype, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                     uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return FUSEML_E_DEVICE;
+  const int eb = dtype_bytes(dtype);
+  CUtensorMapDataType dt = dtype == FUSEML_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                         : dtype == FUSEML_F16  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  // a single row needs no real stride, but the encoder still wants a multiple of 16 bytes
+  int64_t stride_bytes = ld * eb;
+  if (rows == 1) stride_bytes = ((cols * eb + 15) / 16) * 16;
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(stride_bytes)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(tm, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FUSEML_OK : FUSEML_E_LAYOUT;
+}
+
+template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED>
+static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                           cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kernel = gemm_epilogue_kernel<BN, STAGES, FMT, B_MN, SAVED>;
+  static bool configured = false;  // per instantiation; the attribute is sticky per device function
+  static int configured_device = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured || configured_device != dev) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return FUSEML_E_LAUNCH;
+    }
+    configured = true;
+    configured_device = dev;
+  }
+  kernel<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+}
+
+template <int BN, int STAGES>
+static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int fmt, bool b_mn,
+                     int grid, cudaStream_t stream) {
+  const bool saved = p.uses_saved != 0;
+#define FUSEML_DISPATCH(F, MN)                                                              \
+  return saved ? launch_instance<BN, STAGES, F, MN, true>(ta, tb, p, grid, stream)          \
+               : launch_instance<BN, STAGES, F, MN, false>(ta, tb, p, grid, stream)
+  if (fmt == 2) { FUSEML_DISPATCH(2, false); }
+  if (fmt == 1) { if (b_mn) { FUSEML_DISPATCH(1, true); } else { FUSEML_DISPATCH(1, false); } }
+  if (b_mn) { FUSEML_DISPATCH(0, true); } else { FUSEML_DISPATCH(0, false); }
+#undef FUSEML_DISPATCH
+}
+
+static int check_plan(const fuseml_plan_t* pl) {
+  if (pl->tile_m != 128) return FUSEML_E_PLAN;
+  if (pl->tile_n != 128 && pl->tile_n != 256) return FUSEML_E_PLAN;
+  if (pl->grid <= 0 || pl->group_m <= 0) return FUSEML_E_PLAN;
+  if (pl->cluster != 1) return FUSEML_E_PLAN;
+  return FUSEML_OK;
+}
+
+static int run_finalize(const fuseml_reduce_t& r, const WorkspaceLayout& w, char* ws, int64_t count,
+                        cudaStream_t stream) {
+  const float* psum = (r.kinds & (FUSEML_RED_SUM | FUSEML_RED_MEAN)) ? reinterpret_cast<float*>(ws + w.red_sum_off) : nullptr;
+  const float* pmax = (r.kinds & FUSEML_RED_MAX) ? reinterpret_cast<float*>(ws + w.red_max_off) : nullptr;
+  float* o_sum = (r.kinds & FUSEML_RED_SUM) ? r.out_sum : nullptr;
+  float* o_max = (r.kinds & FUSEML_RED_MAX) ? r.out_max : nullptr;
+  float* o_mean = (r.kinds & FUSEML_RED_MEAN) ? r.out_mean : nullptr;
+  const int threads = 256;
+  const int blocks = w.len == 1 ? 1 : static_cast<int>(std::min<int64_t>((w.len + threads - 1) / threads, 1184));
+  reduce_finalize_kernel<<<blocks, threads, 0, stream>>>(psum, pmax, w.partials, w.len, 1.0 / static_cast<double>(count),
+                                                         o_sum, o_max, o_mean);
+  return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+}
+
+}  // namespace fuseml
+
+using namespace fuseml;
+
+extern "C" {
+
+int fuseml_sm100_abi_version(void) { return FUSEML_SM100_ABI_VERSION; }
+
+const char* fuseml_sm100_strerror(int code) {
+  switch (code) {
+    case FUSEML_OK: return "ok";
+    case FUSEML_E_NULL: return "a required pointer is null";
+    case FUSEML_E_SHAPE: return "M, N and K must be positive and below 2^31";
+    case FUSEML_E_DTYPE: return "unsupported dtype";
+    case FUSEML_E_LAYOUT: return "layout not supported: bases must be 16-byte aligned, one unit stride per matrix, leading strides multiples of 16 bytes";
+    case FUSEML_E_EPILOGUE: return "bad epilogue program (opcode, operand slot or length)";
+    case FUSEML_E_REDUCTION: return "bad reduction request";
+    case FUSEML_E_WORKSPACE: return "workspace missing or too small (see fuseml_sm100_workspace_bytes)";
+    case FUSEML_E_PLAN: return "plan fields out of range";
+    case FUSEML_E_DEVICE: return "no sm_100 CUDA device or driver entry point unavailable";
+    case FUSEML_E_LAUNCH: return "CUDA reported an error at launch";
+    case FUSEML_E_TIMEOUT: return "a bounded device-side wait ran out";
+    case FUSEML_E_LIMIT: return "size beyond a documented fixed maximum";
+    default: return "unknown fuseml status code";
+  }
+}
+
+int fuseml_sm100_query(fuseml_device_props_t* props) {
+  if (props == nullptr) return FUSEML_E_NULL;
+  default_props(props);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
+  cudaDeviceProp dp;
+  if (cudaGetDeviceProperties(&dp, dev) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
+  props->sm_count = dp.multiProcessorCount;
+  props->cc_major = dp.major;
+  props->cc_minor = dp.minor;
+  props->smem_per_block_optin = static_cast<int32_t>(dp.sharedMemPerBlockOptin);
+  props->l2_bytes = dp.l2CacheSize;
+  return dp.major == 10 ? FUSEML_OK : FUSEML_E_DEVICE;
+}
+
+int fuseml_sm100_plan(const fuseml_gemm_desc_t* desc, const fuseml_device_props_t* props, fuseml_plan_t* plan) {
+  return make_plan(desc, props, plan);
+}
+
+int fuseml_sm100_validate(const fuseml_gemm_desc_t* desc) { return validate_desc(desc); }
+
+int64_t fuseml_sm100_workspace_bytes(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan) {
+  if (desc == nullptr) return -1;
+  fuseml_plan_t local;
+  if (plan == nullptr) {
+    if (make_plan(desc, nullptr, &local) != FUSEML_OK) return -1;
+    plan = &local;
+  }
+  WorkspaceLayout w;
+  workspace_layout(desc, plan, &w);
+  return w.total;
+}
+
+int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan_in, void* cuda_stream) {
+  int rc = validate_desc(desc);
+  if (rc != FUSEML_OK) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+
+  fuseml_plan_t plan;
+  if (plan_in != nullptr) {
+    plan = *plan_in;
+  } else {
+    fuseml_device_props_t props;
+    if (fuseml_sm100_query(&props) != FUSEML_OK) return FUSEML_E_DEVICE;
+    rc = make_plan(desc, &props, &plan);
+    if (rc != FUSEML_OK) return rc;
+  }
+  rc = check_plan(&plan);
+  if (rc != FUSEML_OK) return rc;
+
+  WorkspaceLayout w;
+  workspace_layout(desc, &plan, &w);
+  char* ws = reinterpret_cast<char*>(desc->reduce.workspace);
+  if (w.total > 0) {
+    if (ws == nullptr || desc->reduce.workspace_bytes < w.total) return FUSEML_E_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(ws) & 15u) != 0) return FUSEML_E_WORKSPACE;
+  }
+
+  const bool f32 = desc->ab_dtype == FUSEML_F32;
+  const int fmt = f32 ? 2 : (desc->ab_dtype == FUSEML_BF16 ? 1 : 0);
+  const int bl = b_layout(desc);
+  const void* a_ptr = desc->a;
+  const void* b_ptr = desc->b;
+  int64_t K = desc->K, lda = desc->lda, ldb = (bl == 0) ? desc->b_stride_n : desc->b_stride_k;
+  bool b_mn = (bl == 1);
+  if (f32) {
+    // expand both operands to [rows, 3K] K-major copies in the workspace
+    const int64_t ld = split_ld(desc->K);
+    float* a2 = reinterpret_cast<float*>(ws + w.split_a_off);
+    float* b2 = reinterpret_cast<float*>(ws + w.split_b_off);
+    const int threads = 256;
+    const int64_t ta = desc->M * desc->K, tb = desc->N * desc->K;
+    const int ga = static_cast<int>(std::min<int64_t>((ta + threads - 1) / threads, 148 * 16));
+    const int gb = static_cast<int>(std::min<int64_t>((tb + threads - 1) / threads, 148 * 16));
+    split_tf32_kernel<<<ga, threads, 0, stream>>>(reinterpret_cast<const float*>(desc->a), desc->M, desc->K,
+                                                  desc->lda, 1, 0, a2, ld);
+    split_tf32_kernel<<<gb, threads, 0, stream>>>(reinterpret_cast<const float*>(desc->b), desc->N, desc->K,
+                                                  desc->b_stride_n, desc->b_stride_k, 1, b2, ld);
+    if (cudaGetLastError() != cudaSuccess) return FUSEML_E_LAUNCH;
+    a_ptr = a2; b_ptr = b2; K = 3 * desc->K; lda = ld; ldb = ld; b_mn = false;
+  }
+
+  const int BN = plan.tile_n;
+  const int BK = f32 ? 32 : 64;
+  CUtensorMap ta, tb;
+  rc = encode_2d(&ta, desc->ab_dtype, a_ptr, desc->M, K, lda, BK, kTileM);
+  if (rc != FUSEML_OK) return rc;
+  if (!b_mn) rc = encode_2d(&tb, desc->ab_dtype, b_ptr, desc->N, K, ldb, BK, BN);
+  else rc = encode_2d(&tb, desc->ab_dtype, b_ptr, K, desc->N, ldb, 64, BK);
+  if (rc != FUSEML_OK) return rc;
+
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.M = static_cast<int32_t>(desc->M);
+  p.N = static_cast<int32_t>(desc->N);
+  p.K = static_cast<int32_t>(K);
+  p.tiles_m = static_cast<int32_t>((desc->M + kTileM - 1) / kTileM);
+  p.tiles_n = static_cast<int32_t>((desc->N + BN - 1) / BN);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.group_m = std::min(plan.group_m, p.tiles_m);
+  p.num_kb = static_cast<int32_t>((K + BK - 1) / BK);
+  p.d = desc->d;
+  p.ldd = desc->ldd;
+  p.out_dtype = desc->out_dtype;
+  p.n_ops = desc->n_ops;
+  for (int i = 0; i < desc->n_ops; ++i) {
+    p.ops[i] = desc->ops[i];
+    const int32_t oc = desc->ops[i].opcode;
+    if (oc == FUSEML_OP_SAVE || oc == FUSEML_OP_SWAP || oc == FUSEML_OP_ADD_SAVED || oc == FUSEML_OP_MUL_SAVED)
+      p.uses_saved = 1;
+  }
+  for (int i = 0; i < desc->n_operands; ++i) {
+    p.operands[i].ptr = desc->operands[i].ptr;
+    p.operands[i].stride_m = desc->operands[i].stride_m;
+    p.operands[i].stride_n = desc->operands[i].stride_n;
+    p.operands[i].dtype = desc->operands[i].dtype;
+  }
+  p.red_kinds = desc->reduce.kinds;
+  p.red_axis = desc->reduce.axis;
+  if (desc->reduce.kinds != 0) {
+    if (desc->reduce.kinds & (FUSEML_RED_SUM | FUSEML_RED_MEAN)) p.red_sum = reinterpret_cast<float*>(ws + w.red_sum_off);
+    if (desc->reduce.kinds & FUSEML_RED_MAX) p.red_max = reinterpret_cast<float*>(ws + w.red_max_off);
+  }
+  void* status_ptr = nullptr;
+  if (cudaGetSymbolAddress(&status_ptr, g_status_word) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
+  p.status = reinterpret_cast<int32_t*>(status_ptr);
+
+  int grid = std::min(plan.grid, p.num_tiles);
+  if (desc->reduce.kinds != 0 && desc->reduce.axis == FUSEML_AXIS_ALL) grid = std::min<int>(grid, static_cast<int>(w.partials));
+  if (BN == 256) rc = launch_bn<256, 4>(ta, tb, p, fmt, b_mn, grid, stream);
+  else rc = launch_bn<128, 6>(ta, tb, p, fmt, b_mn, grid, stream);
+  if (rc != FUSEML_OK) return rc;
+
+  if (desc->reduce.kinds != 0) {
+    // AXIS_ALL partials: one per launched CTA
+    if (desc->reduce.axis == FUSEML_AXIS_ALL) w.partials = grid;
+    const int64_t count = desc->reduce.axis == FUSEML_AXIS_N ? desc->N
+                        : desc->reduce.axis == FUSEML_AXIS_M ? desc->M : desc->M * desc->N;
+    rc = run_finalize(desc->reduce, w, ws, count, stream);
+  }
+  return rc;
+}
+
+int fuseml_sm100_reduce_tail(const void* x, int32_t dtype, int64_t M, int64_t N, int64_t ldx,
+                             const fuseml_reduce_t* r, void* cuda_stream) {
+  if (x == nullptr || r == nullptr) return FUSEML_E_NULL;
+  if (M <= 0 || N <= 0 || ldx < N) return FUSEML_E_SHAPE;
+  if (dtype_bytes(dtype) == 0) return FUSEML_E_DTYPE;
+  if (r->kinds == 0 || (r->kinds & ~7)) return FUSEML_E_REDUCTION;
+  if ((r->kinds & FUSEML_RED_SUM) && !r->out_sum) return FUSEML_E_NULL;
+  if ((r->kinds & FUSEML_RED_MAX) && !r->out_max) return FUSEML_E_NULL;
+  if ((r->kinds & FUSEML_RED_MEAN) && !r->out_mean) return FUSEML_E_NULL;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  const bool want_sum = (r->kinds & (FUSEML_RED_SUM | FUSEML_RED_MEAN)) != 0;
+  const bool want_max = (r->kinds & FUSEML_RED_MAX) != 0;
+  if (r->axis == FUSEML_AXIS_N) {
+    const int grid = static_cast<int>(std::min<int64_t>(M, 148 * 8));
+    reduce_rows_kernel<<<grid, 256, 0, stream>>>(x, dtype, M, N, ldx, 0, 1.0 / static_cast<double>(N),
+                                                 (r->kinds & FUSEML_RED_SUM) ? r->out_sum : nullptr,
+                                                 want_max ? r->out_max : nullptr,
+                                                 (r->kinds & FUSEML_RED_MEAN) ? r->out_mean : nullptr);
+    return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+  }
+  // partials through the workspace
+  WorkspaceLayout w;
+  std::memset(&w, 0, sizeof(w));
+  int64_t rows_per_slice = 0;
+  if (r->axis == FUSEML_AXIS_ALL) { w.partials = std::min<int64_t>(M, 148 * 8); w.len = 1; }
+  else if (r->axis == FUSEML_AXIS_M) {
+    const int64_t slices = std::max<int64_t>(1, std::min<int64_t>((M + 63) / 64, 64));
+    rows_per_slice = (M + slices - 1) / slices;
+    w.partials = (M + rows_per_slice - 1) / rows_per_slice; w.len = N;
+  } else return FUSEML_E_REDUCTION;
+  int64_t off = 0;
+  const int64_t each = ((w.partials * w.len * 4 + 255) / 256) * 256;
+  if (want_sum) { w.red_sum_off = off; off += each; }
+  if (want_max) { w.red_max_off = off; off += each; }
+  char* ws = reinterpret_cast<char*>(r->workspace);
+  if (ws == nullptr || r->workspace_bytes < off) return FUSEML_E_WORKSPACE;
+  float* psum = want_sum ? reinterpret_cast<float*>(ws + w.red_sum_off) : nullptr;
+  float* pmax = want_max ? reinterpret_cast<float*>(ws + w.red_max_off) : nullptr;
+  if (r->axis == FUSEML_AXIS_ALL) {
+    reduce_rows_kernel<<<static_cast<int>(w.partials), 256, 0, stream>>>(x, dtype, M, N, ldx, 1, 0.0, psum, pmax, nullptr);
+  } else {
+    dim3 grid(static_cast<unsigned>((N + 255) / 256), static_cast<unsigned>(w.partials));
+    reduce_cols_kernel<<<grid, 256, 0, stream>>>(x, dtype, M, N, ldx, rows_per_slice, psum, pmax);
+  }
+  if (cudaGetLastError() != cudaSuccess) return FUSEML_E_LAUNCH;
+  const int64_t count = r->axis == FUSEML_AXIS_M ? M : M * N;
+  return run_finalize(*r, w, ws, count, stream);
+}
+
+int fuseml_sm100_device_status(void* cuda_stream, int32_t* status_out) {
+  if (status_out == nullptr) return FUSEML_E_NULL;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  int32_t v = 0;
+  if (cudaMemcpyFromSymbolAsync(&v, g_status_word, sizeof(v), 0, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess) {
+    cudaGetLastError();
+    return FUSEML_E_LAUNCH;
+  }
+  *status_out = v;
+  if (v != 0) {
+    const int32_t zero = 0;
+    cudaMemcpyToSymbolAsync(g_status_word, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, stream);
+    cudaStreamSynchronize(stream);
+    return FUSEML_E_TIMEOUT;
+  }
+  return FUSEML_OK;
+}
+
+}  // extern "C"

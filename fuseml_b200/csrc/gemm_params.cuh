@@ -1,0 +1,62 @@
+// Device-side parameter block of the fused GEMM kernels.  It is filled on the
+// host from the public fuseml_gemm_desc_t + fuseml_plan_t and passed by value
+// (kernel parameter space), so a launch reads no host memory and needs no
+// device-side allocation.
+#pragma once
+
+#include <stdint.h>
+
+#include "../../include/fuseml_sm100.h"
+
+namespace fuseml {
+
+constexpr int kTileM = 128;        // UMMA M with cta_group::1: one TMEM lane per row
+constexpr int kSwizzleBytes = 128; // K extent of one shared-memory stage, in bytes
+constexpr int kNumThreads = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
+constexpr int kEpilogueWarps = 4;
+constexpr int kChunkN = 32;        // accumulator columns one tcgen05.ld brings in
+
+struct EpiOperand {
+  const void* ptr;
+  int64_t stride_m;
+  int64_t stride_n;
+  int32_t dtype;
+  int32_t writable;
+};
+
+struct GemmParams {
+  int32_t M, N, K;
+  int32_t tiles_m, tiles_n, num_tiles, group_m, num_kb;
+  void* d;           // may be null (reduction-only chains)
+  int64_t ldd;
+  int32_t out_dtype;
+  int32_t n_ops;
+  fuseml_epi_op_t ops[FUSEML_MAX_EPI_OPS];
+  EpiOperand operands[FUSEML_MAX_OPERANDS];
+  // reductions: partials go to `red_sum` / `red_max` (inside the caller's
+  // workspace); a finalize kernel folds them afterwards.
+  int32_t red_kinds;
+  int32_t red_axis;
+  float* red_sum;    // [partials][len]
+  float* red_max;    // [partials][len]
+  int32_t uses_saved;  // program contains SAVE/SWAP/*_SAVED
+  int32_t* status;     // device status word (bounded-wait time-outs)
+};
+
+// Tile id -> (tile row, tile column).  Tiles are walked in groups of
+// `group_m` tile rows: CTAs that run at the same time then share a narrow band
+// of B columns and a short stack of A row blocks, which keeps both resident in
+// L2 (same idea as the GROUP_SIZE_M swizzle of the reference,
+// fuseml/codegen/kernel_generator.py:1278-1286).
+__host__ __device__ inline void tile_coords(int32_t t, int32_t tiles_m, int32_t tiles_n, int32_t group_m,
+                                            int32_t* tm, int32_t* tn) {
+  const int32_t group_size = group_m * tiles_n;
+  const int32_t group_id = t / group_size;
+  const int32_t first_m = group_id * group_m;
+  const int32_t rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+  const int32_t r = t - group_id * group_size;
+  *tm = first_m + (r % rows);
+  *tn = r / rows;
+}
+
+}  // namespace fuseml

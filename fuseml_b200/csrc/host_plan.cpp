@@ -1,0 +1,239 @@
+// Host-only part of the C ABI: descriptor validation, the roofline router that
+// picks tile / stage / cluster shapes, and the workspace arithmetic.  No CUDA
+// call is made here, so these functions work (and are tested) on a machine
+// without a GPU.
+//
+// The router replaces the reference's three-tier cost model
+// (fuseml/passes/topology.py:479-571: penalty-vs-savings with per-arch tables;
+// fuseml/passes/fusion_pass.py:463-498: the M*N < 500000 "tiny" bypass;
+// fuseml/codegen/cublas_epilogue.py:166-258: the cuBLAS Lt pattern match) and the
+// analytic SRAM autotuner (fuseml/codegen/sram_autotuner.py:135-213, 336-437).
+// There is a single tier here - the fused sm_100a kernel - so the router only
+// decides *how* to run it and predicts the time from the roofline.
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+#include "host_plan.h"
+
+namespace fuseml {
+
+int dtype_bytes(int32_t dt) {
+  switch (dt) {
+    case FUSEML_BF16:
+    case FUSEML_F16:
+      return 2;
+    case FUSEML_F32:
+      return 4;
+    default:
+      return 0;
+  }
+}
+
+void default_props(fuseml_device_props_t* p) {
+  p->sm_count = 148;
+  p->cc_major = 10;
+  p->cc_minor = 0;
+  p->smem_per_block_optin = 232448;  // 227 KB
+  p->tmem_cols = 512;
+  p->l2_bytes = 126 * 1024 * 1024;
+  p->hbm_gbs = 7700.0;               // HGX B200 HBM3e
+  p->tensor_tflops = 2250.0;         // dense bf16
+}
+
+static bool op_uses_operand(int32_t opcode) {
+  return opcode == FUSEML_OP_ADD_T || opcode == FUSEML_OP_MUL_T || opcode == FUSEML_OP_SUB_T ||
+         opcode == FUSEML_OP_RSUB_T || opcode == FUSEML_OP_STORE_AUX;
+}
+
+int b_layout(const fuseml_gemm_desc_t* d) {
+  const int eb = dtype_bytes(d->ab_dtype);
+  const bool tma = d->ab_dtype != FUSEML_F32;
+  if (d->b_stride_k == 1) {
+    if (d->N == 1) return 0;
+    if (d->b_stride_n >= d->K && (!tma || (d->b_stride_n * eb) % 16 == 0)) return 0;
+  }
+  if (d->b_stride_n == 1) {
+    if (d->K == 1) return 1;
+    if (d->b_stride_k >= d->N && (!tma || (d->b_stride_k * eb) % 16 == 0)) return 1;
+  }
+  return -1;
+}
+
+int validate_desc(const fuseml_gemm_desc_t* d) {
+  if (d == nullptr) return FUSEML_E_NULL;
+  if (d->a == nullptr || d->b == nullptr) return FUSEML_E_NULL;
+  if (d->M <= 0 || d->N <= 0 || d->K <= 0) return FUSEML_E_SHAPE;
+  if (d->M > 0x7fffff00ll || d->N > 0x7fffff00ll || d->K > 0x2a000000ll) return FUSEML_E_SHAPE;
+  const int eb = dtype_bytes(d->ab_dtype);
+  if (eb == 0) return FUSEML_E_DTYPE;
+  if (dtype_bytes(d->out_dtype) == 0) return FUSEML_E_DTYPE;
+  if (d->ab_dtype != FUSEML_F32) {
+    // TMA reads A and B directly: 16-byte aligned base, leading stride a multiple of
+    // 16 bytes.  (fp32 operands are first expanded by a plain-load kernel, so any
+    // stride works there.)
+    if ((reinterpret_cast<uintptr_t>(d->a) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d->b) & 15u) != 0)
+      return FUSEML_E_LAYOUT;
+    if (d->M > 1 && (d->lda < d->K || (d->lda * eb) % 16 != 0)) return FUSEML_E_LAYOUT;
+  } else if (d->M > 1 && d->lda < d->K) {
+    return FUSEML_E_LAYOUT;
+  }
+  if (b_layout(d) < 0) return FUSEML_E_LAYOUT;
+  if (d->n_ops < 0 || d->n_ops > FUSEML_MAX_EPI_OPS) return FUSEML_E_EPILOGUE;
+  if (d->n_operands < 0 || d->n_operands > FUSEML_MAX_OPERANDS) return FUSEML_E_EPILOGUE;
+  for (int i = 0; i < d->n_ops; ++i) {
+    const fuseml_epi_op_t& op = d->ops[i];
+    if (op.opcode < 0 || op.opcode >= FUSEML_OP__COUNT) return FUSEML_E_EPILOGUE;
+    if (op_uses_operand(op.opcode)) {
+      if (op.slot < 0 || op.slot >= d->n_operands) return FUSEML_E_EPILOGUE;
+      const fuseml_operand_t& o = d->operands[op.slot];
+      if (o.ptr == nullptr) return FUSEML_E_NULL;
+      if (dtype_bytes(o.dtype) == 0) return FUSEML_E_DTYPE;
+      if (o.stride_m < 0 || o.stride_n < 0) return FUSEML_E_LAYOUT;
+      if (op.opcode == FUSEML_OP_STORE_AUX && (o.stride_n != 1 || o.stride_m < d->N)) return FUSEML_E_LAYOUT;
+    }
+  }
+  const fuseml_reduce_t& r = d->reduce;
+  if (r.kinds != 0) {
+    if (r.kinds & ~(FUSEML_RED_SUM | FUSEML_RED_MAX | FUSEML_RED_MEAN)) return FUSEML_E_REDUCTION;
+    if (r.axis != FUSEML_AXIS_N && r.axis != FUSEML_AXIS_M && r.axis != FUSEML_AXIS_ALL)
+      return FUSEML_E_REDUCTION;
+    if ((r.kinds & FUSEML_RED_SUM) && r.out_sum == nullptr) return FUSEML_E_NULL;
+    if ((r.kinds & FUSEML_RED_MAX) && r.out_max == nullptr) return FUSEML_E_NULL;
+    if ((r.kinds & FUSEML_RED_MEAN) && r.out_mean == nullptr) return FUSEML_E_NULL;
+  } else if (d->d == nullptr) {
+    return FUSEML_E_NULL;  // nothing to produce
+  }
+  if (d->d != nullptr && d->ldd < d->N) return FUSEML_E_LAYOUT;
+  return FUSEML_OK;
+}
+
+static int64_t round_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+int64_t split_ld(int64_t K) { return round_up(3 * K, 4); }
+
+static double operand_bytes(const fuseml_gemm_desc_t* d) {
+  double b = 0.0;
+  bool seen[FUSEML_MAX_OPERANDS] = {false};
+  for (int i = 0; i < d->n_ops; ++i) {
+    const fuseml_epi_op_t& op = d->ops[i];
+    if (!op_uses_operand(op.opcode) || op.slot < 0 || op.slot >= d->n_operands || seen[op.slot]) continue;
+    seen[op.slot] = true;
+    const fuseml_operand_t& o = d->operands[op.slot];
+    const double rows = o.stride_m == 0 ? 1.0 : static_cast<double>(d->M);
+    const double cols = o.stride_n == 0 ? 1.0 : static_cast<double>(d->N);
+    b += rows * cols * dtype_bytes(o.dtype);
+  }
+  return b;
+}
+
+int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in, fuseml_plan_t* plan) {
+  if (d == nullptr || plan == nullptr) return FUSEML_E_NULL;
+  std::memset(plan, 0, sizeof(*plan));
+  const int v = validate_desc(d);
+  fuseml_device_props_t props;
+  if (props_in) props = *props_in; else default_props(&props);
+
+  const int eb = std::max(1, dtype_bytes(d->ab_dtype));
+  const bool f32 = d->ab_dtype == FUSEML_F32;
+  const double M = static_cast<double>(d->M), N = static_cast<double>(d->N), K = static_cast<double>(d->K);
+  plan->flops = 2.0 * M * N * K;
+  double bytes = M * K * eb + K * N * eb + operand_bytes(d);
+  if (d->d != nullptr) bytes += M * N * std::max(1, dtype_bytes(d->out_dtype));
+  if (d->reduce.kinds != 0) {
+    const double len = d->reduce.axis == FUSEML_AXIS_N ? M : (d->reduce.axis == FUSEML_AXIS_M ? N : 1.0);
+    int kinds = 0;
+    for (int b = 1; b <= 4; b <<= 1) kinds += (d->reduce.kinds & b) ? 1 : 0;
+    bytes += len * 4.0 * kinds;
+  }
+  plan->bytes = bytes;
+  // fp32 operands run as three TF32 products (hi*hi + lo*hi + hi*lo): 3x the MMA work
+  const double mma_flops = plan->flops * (f32 ? 3.0 : 1.0);
+  const double tc_rate = props.tensor_tflops * (f32 ? 0.5 : 1.0);  // TF32 runs at half the bf16 rate
+  plan->t_tensor_us = mma_flops / (tc_rate * 1e12) * 1e6;
+  plan->t_hbm_us = bytes / (props.hbm_gbs * 1e9) * 1e6;
+
+  plan->tile_m = 128;
+  plan->tile_k = 128 / (f32 ? 4 : eb);
+  plan->cluster = 1;
+  plan->acc_stages = 2;
+
+  // Candidate tile widths; pick the one with the smaller estimated time
+  // (per-tile tensor time x waves, against the HBM time).
+  const int64_t tiles_m = (d->M + 127) / 128;
+  const double per_sm_rate = tc_rate * 1e12 / std::max(1, props.sm_count);
+  const int64_t k_eff = (f32 ? 3 : 1) * d->K;
+  const int64_t k_pad = round_up(k_eff, plan->tile_k);
+  double best = 1e300;
+  int best_bn = 256;
+  const int candidates[2] = {256, 128};
+  for (int ci = 0; ci < 2; ++ci) {
+    const int bn = candidates[ci];
+    const int64_t tiles_n = (d->N + bn - 1) / bn;
+    const int64_t tiles = tiles_m * tiles_n;
+    const int64_t waves = (tiles + props.sm_count - 1) / props.sm_count;
+    const double t_tile = 2.0 * 128.0 * bn * static_cast<double>(k_pad) / per_sm_rate * 1e6;
+    // narrower tiles re-read A more often from L2 and keep the tensor pipe less busy per
+    // shared-memory byte: a 5 % handicap keeps 256 the default when the wave counts tie
+    const double t = std::max(waves * t_tile * (bn == 128 ? 1.05 : 1.0), plan->t_hbm_us);
+    if (t < best) { best = t; best_bn = bn; }
+  }
+  plan->tile_n = best_bn;
+  const int64_t tiles_n = (d->N + best_bn - 1) / best_bn;
+  const int64_t tiles = tiles_m * tiles_n;
+  plan->grid = static_cast<int32_t>(std::min<int64_t>(tiles, props.sm_count));
+  plan->group_m = static_cast<int32_t>(std::min<int64_t>(8, tiles_m));
+
+  // Shared memory: ring of (A 16 KB + B tile_n*128 B) stages under the opt-in budget.
+  const int stage_bytes = 128 * 128 + best_bn * 128;
+  const int fixed = 4 * best_bn * 2 * 4 /* column-reduction scratch */ + 256 /* barriers */ + 1024 /* alignment */;
+  int stages = (props.smem_per_block_optin - fixed) / stage_bytes;
+  stages = std::max(2, std::min(stages, best_bn == 256 ? 4 : 6));
+  plan->stages = stages;
+  plan->smem_bytes = stages * stage_bytes + fixed;
+  plan->tmem_cols = 2 * best_bn;
+
+  const double launch_us = 3.0;
+  plan->t_est_us = best + launch_us;
+  if (plan->t_est_us < 2.0 * launch_us) plan->bound = 2;
+  else plan->bound = (plan->t_tensor_us >= plan->t_hbm_us) ? 1 : 0;
+  plan->fuse = (v == FUSEML_OK) ? 1 : 0;
+  return v;
+}
+
+static int64_t align256(int64_t x) { return round_up(x, 256); }
+
+void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, WorkspaceLayout* w) {
+  std::memset(w, 0, sizeof(*w));
+  int64_t off = 0;
+  if (d->ab_dtype == FUSEML_F32) {
+    const int64_t ld = split_ld(d->K);
+    w->split_a_off = off;
+    off += align256(d->M * ld * 4);
+    w->split_b_off = off;
+    off += align256(d->N * ld * 4);
+  }
+  if (d->reduce.kinds != 0) {
+    const int64_t tiles_m = (d->M + plan->tile_m - 1) / plan->tile_m;
+    const int64_t tiles_n = (d->N + plan->tile_n - 1) / plan->tile_n;
+    int64_t partials, len;
+    if (d->reduce.axis == FUSEML_AXIS_N) { partials = tiles_n; len = d->M; }
+    else if (d->reduce.axis == FUSEML_AXIS_M) { partials = tiles_m; len = d->N; }
+    else { partials = plan->grid; len = 1; }
+    w->partials = partials;
+    w->len = len;
+    if (d->reduce.kinds & (FUSEML_RED_SUM | FUSEML_RED_MEAN)) {
+      w->red_sum_off = off;
+      off += align256(partials * len * 4);
+    }
+    if (d->reduce.kinds & FUSEML_RED_MAX) {
+      w->red_max_off = off;
+      off += align256(partials * len * 4);
+    }
+  }
+  w->total = off;
+}
+
+}  // namespace fuseml

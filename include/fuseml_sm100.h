@@ -1,0 +1,233 @@
+/*
+ * fuseml_sm100.h — C ABI of the sm_100a fused GEMM + epilogue backend.
+ *
+ * This is the boundary a FuseML maintainer binds in place of the Triton /
+ * cuBLAS Lt back half of the reference.  Every entry point takes plain
+ * pointers, sizes and strides (no torch types), never allocates or frees
+ * device memory, enqueues its work on the CUDA stream it is given and
+ * returns without synchronising the host.  Return value: 0 on success, one
+ * of the FUSEML_E_* codes otherwise (text via fuseml_sm100_strerror).
+ *
+ * Reference interfaces replaced (paths inside the FuseML source tree):
+ *   - the generated Triton kernel's flat argument list
+ *     (fuseml/codegen/kernel_generator.py:695-819, kernel ABI;
+ *      fuseml/codegen/kernel_launcher.py:766-814, the launch call)
+ *   - aten._addmm_activation / the inline cublasLt addmm_bias_residual
+ *     (fuseml/codegen/cublas_epilogue.py:355-571, 602-676)
+ *   - the three-tier cost model
+ *     (fuseml/passes/topology.py:479-571, fuseml/passes/fusion_pass.py:382-498)
+ *   - the SRAM autotuner footprint model
+ *     (fuseml/codegen/sram_autotuner.py:135-213)
+ */
+#ifndef FUSEML_SM100_H_
+#define FUSEML_SM100_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FUSEML_SM100_ABI_VERSION 1
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+  FUSEML_OK = 0,
+  FUSEML_E_NULL = 1,          /* a required pointer is null                     */
+  FUSEML_E_SHAPE = 2,         /* M, N or K is not positive / exceeds int32      */
+  FUSEML_E_DTYPE = 3,         /* dtype combination not supported                */
+  FUSEML_E_LAYOUT = 4,        /* stride / alignment not expressible as a TMA map*/
+  FUSEML_E_EPILOGUE = 5,      /* unknown opcode, bad operand slot, too many ops */
+  FUSEML_E_REDUCTION = 6,     /* bad reduction request                          */
+  FUSEML_E_WORKSPACE = 7,     /* workspace missing or too small                 */
+  FUSEML_E_PLAN = 8,          /* plan fields out of range                       */
+  FUSEML_E_DEVICE = 9,        /* no sm_100 device / driver entry point missing  */
+  FUSEML_E_LAUNCH = 10,       /* CUDA reported an error at launch               */
+  FUSEML_E_TIMEOUT = 11,      /* a bounded device-side wait ran out             */
+  FUSEML_E_LIMIT = 12         /* size beyond a documented fixed maximum         */
+};
+
+/* ---- element types ------------------------------------------------------ */
+enum {
+  FUSEML_BF16 = 0,
+  FUSEML_F16 = 1,
+  FUSEML_F32 = 2
+};
+
+/* ---- epilogue opcodes ---------------------------------------------------
+ * The epilogue is a short program run on the fp32 accumulator tile while it
+ * is still in registers (the reference emits the same operations as Triton
+ * source, fuseml/codegen/kernel_generator.py:1599-1903).  Two value
+ * registers exist per element: `acc` and `saved`; SAVE/SWAP/…_SAVED express
+ * single-entry DAGs such as gelu(h) * sigmoid(h).
+ */
+enum {
+  FUSEML_OP_NOP = 0,
+  FUSEML_OP_RELU = 1,        /* acc = acc > 0 ? acc : 0      (kernel_generator.py:1604) */
+  FUSEML_OP_GELU_ERF = 2,    /* 0.5*acc*(1+erf(acc/sqrt2))   (kernel_generator.py:1641) */
+  FUSEML_OP_SIGMOID = 3,     /* 1/(1+exp(-acc))              (kernel_generator.py:1655) */
+  FUSEML_OP_ADD_IMM = 4,     /* acc += imm                                              */
+  FUSEML_OP_MUL_IMM = 5,     /* acc *= imm                                              */
+  FUSEML_OP_ADD_T = 6,       /* acc += operand[slot][m,n]  (any stride, 0 = broadcast)  */
+  FUSEML_OP_MUL_T = 7,       /* acc *= operand[slot][m,n]                               */
+  FUSEML_OP_SAVE = 8,        /* saved = acc                                             */
+  FUSEML_OP_SWAP = 9,        /* (acc, saved) = (saved, acc)                             */
+  FUSEML_OP_ADD_SAVED = 10,  /* acc += saved                                            */
+  FUSEML_OP_MUL_SAVED = 11,  /* acc *= saved                                            */
+  FUSEML_OP_GELU_TANH = 12,  /* tanh-approximate GELU (aten.gelu approximate='tanh')    */
+  FUSEML_OP_STORE_AUX = 13,  /* aux[slot][m,n] = acc (escape store of an intermediate,  */
+                             /*   kernel_generator.py:2020-2039); operand must be       */
+                             /*   writable, row-major, same dtype rules as the output   */
+  FUSEML_OP_SUB_T = 14,      /* acc -= operand[slot][m,n]                               */
+  FUSEML_OP_RSUB_T = 15,     /* acc = operand[slot][m,n] - acc                          */
+  FUSEML_OP__COUNT = 16
+};
+
+#define FUSEML_MAX_EPI_OPS 16
+#define FUSEML_MAX_OPERANDS 8
+
+typedef struct {
+  int32_t opcode;  /* FUSEML_OP_*                              */
+  int32_t slot;    /* operand index for *_T / STORE_AUX, else 0 */
+  float imm;       /* immediate for *_IMM                       */
+  int32_t reserved;
+} fuseml_epi_op_t;
+
+/* A 2-D view addressed as ptr[m*stride_m + n*stride_n] (strides in
+ * elements; 0 broadcasts that dimension — covers bias[N] (stride_m = 0),
+ * per-row vectors (stride_n = 0), expand()ed tensors and full [M,N]
+ * residuals (kernel_generator.py:1659-1743). */
+typedef struct {
+  const void* ptr;
+  int64_t stride_m;
+  int64_t stride_n;
+  int32_t dtype;   /* FUSEML_BF16 | FUSEML_F16 | FUSEML_F32 */
+  int32_t reserved;
+} fuseml_operand_t;
+
+/* ---- reductions --------------------------------------------------------- */
+enum {
+  FUSEML_RED_SUM = 1,
+  FUSEML_RED_MAX = 2,
+  FUSEML_RED_MEAN = 4
+};
+enum {
+  FUSEML_AXIS_N = 1,   /* reduce over columns -> one value per row, out[M]  (dim=-1) */
+  FUSEML_AXIS_M = 0,   /* reduce over rows    -> one value per column, out[N] (dim=0) */
+  FUSEML_AXIS_ALL = 2  /* reduce over the whole tile grid -> one scalar              */
+};
+
+typedef struct {
+  int32_t kinds;        /* bit-or of FUSEML_RED_*; 0 = no reduction             */
+  int32_t axis;         /* FUSEML_AXIS_*                                        */
+  float* out_sum;       /* fp32 outputs, one per requested kind                 */
+  float* out_max;
+  float* out_mean;
+  void* workspace;      /* caller-owned scratch, see fuseml_sm100_workspace_bytes */
+  int64_t workspace_bytes;
+} fuseml_reduce_t;
+
+/* ---- the GEMM problem --------------------------------------------------- */
+typedef struct {
+  int64_t M, N, K;
+  /* A[M,K]: element (m,k) at a[m*lda + k]; K contiguous.                     */
+  const void* a;
+  int64_t lda;
+  /* B[K,N]: element (k,n) at b[k*b_stride_k + n*b_stride_n]; exactly one of
+   * the strides is 1.  b_stride_k == 1 is the nn.Linear weight view
+   * (aten.t of W[N,K]); b_stride_n == 1 is a row-major [K,N] matrix.         */
+  const void* b;
+  int64_t b_stride_k;
+  int64_t b_stride_n;
+  int32_t ab_dtype;     /* FUSEML_BF16 | FUSEML_F16 | FUSEML_F32 (F32 runs as TF32x3) */
+  int32_t out_dtype;    /* dtype of d                                                 */
+  /* D[M,N] row-major, leading dimension ldd; may be null when the chain ends
+   * in a reduction and the matrix itself is never needed.                    */
+  void* d;
+  int64_t ldd;
+  /* epilogue program                                                         */
+  int32_t n_ops;
+  int32_t n_operands;
+  fuseml_epi_op_t ops[FUSEML_MAX_EPI_OPS];
+  fuseml_operand_t operands[FUSEML_MAX_OPERANDS];
+  fuseml_reduce_t reduce;
+} fuseml_gemm_desc_t;
+
+/* ---- plan: what the roofline router decides ----------------------------- */
+typedef struct {
+  int32_t tile_m;        /* 128                                              */
+  int32_t tile_n;        /* 64 | 128 | 256                                   */
+  int32_t tile_k;        /* elements per smem stage (128 bytes of K)         */
+  int32_t stages;        /* depth of the TMA -> MMA shared-memory ring       */
+  int32_t cluster;       /* CTAs cooperating on one MMA (1 or 2)             */
+  int32_t acc_stages;    /* TMEM accumulator buffers (epilogue overlap)      */
+  int32_t grid;          /* persistent CTAs launched                         */
+  int32_t group_m;       /* rasterisation group (tiles along M per sweep)    */
+  int32_t smem_bytes;    /* dynamic shared memory requested                  */
+  int32_t tmem_cols;     /* TMEM columns allocated per CTA                   */
+  int32_t bound;         /* 0 = HBM-bound, 1 = tensor-bound, 2 = latency     */
+  int32_t fuse;          /* 1 = run fused kernel, 0 = router declines        */
+  double flops;          /* 2*M*N*K                                          */
+  double bytes;          /* algorithmic HBM bytes                            */
+  double t_tensor_us;    /* flops / tensor peak                              */
+  double t_hbm_us;       /* bytes / HBM peak                                 */
+  double t_est_us;       /* roofline estimate incl. wave quantisation        */
+} fuseml_plan_t;
+
+typedef struct {
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;
+  int32_t smem_per_block_optin;   /* bytes */
+  int32_t tmem_cols;              /* 512 on sm_100 */
+  int32_t l2_bytes;
+  double hbm_gbs;                 /* peak used by the router */
+  double tensor_tflops;           /* dense bf16 peak used by the router */
+} fuseml_device_props_t;
+
+/* Fills props for the current device; with no CUDA device it fills the
+ * published B200 figures and returns FUSEML_E_DEVICE.
+ * Replaces topology._get_gpu_specs (fuseml/passes/topology.py:386-458). */
+int fuseml_sm100_query(fuseml_device_props_t* props);
+
+/* Host-only: choose tile / stage / cluster shape and estimate the run time
+ * from a roofline model.  `props` may be null (B200 defaults).
+ * Replaces is_compute_bound_gemm (fuseml/passes/topology.py:479-571),
+ * _is_tiny_output/_is_compute_bound_trigger (fuseml/passes/fusion_pass.py:382-498)
+ * and SRAMAutotuner.get_best_config (fuseml/codegen/sram_autotuner.py:220-447). */
+int fuseml_sm100_plan(const fuseml_gemm_desc_t* desc, const fuseml_device_props_t* props,
+                      fuseml_plan_t* plan);
+
+/* Bytes of caller-provided scratch the described launch needs (0 when the
+ * chain has no reduction and the operands are not fp32). */
+int64_t fuseml_sm100_workspace_bytes(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan);
+
+/* Host-only validation of a descriptor (what the launch would check first). */
+int fuseml_sm100_validate(const fuseml_gemm_desc_t* desc);
+
+/* D = epilogue(A @ B) and/or its reductions, one fused kernel (+ a small
+ * finalize kernel when a reduction is requested).  `plan` may be null.
+ * Replaces fused_kernel[grid](...) (fuseml/codegen/kernel_launcher.py:811-814),
+ * aten._addmm_activation (fuseml/codegen/cublas_epilogue.py:613-616) and
+ * addmm_bias_residual (fuseml/codegen/cublas_epilogue.py:396-557). */
+int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan,
+                               void* cuda_stream);
+
+/* Stand-alone reduction tail over an existing [M,N] matrix (used when the
+ * reduction cannot be absorbed into the producing GEMM): sum / max / mean
+ * over rows, columns or everything; fp32 results.  Replaces the eager
+ * aten.sum/amax/mean tails the reference leaves in the graph when a reduction
+ * is not absorbed (fuseml/passes/fusion_pass.py:205-241). */
+int fuseml_sm100_reduce_tail(const void* x, int32_t dtype, int64_t M, int64_t N, int64_t ldx,
+                             const fuseml_reduce_t* reduce, void* cuda_stream);
+
+/* Reads and clears the device-side status word written by bounded waits.
+ * Synchronises the given stream.  0 = no kernel gave up. */
+int fuseml_sm100_device_status(void* cuda_stream, int32_t* status_out);
+
+const char* fuseml_sm100_strerror(int code);
+int fuseml_sm100_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSEML_SM100_H_ */
