@@ -1,0 +1,499 @@
+#!/usr/bin/env python
+"""Benchmark of the fused GEMM + epilogue path on B200.
+
+``python bench.py --gpus N --steps K --warmup W`` runs the residual Transformer-MLP
+block (d_model 4096, d_intermediate 16384, 8192 tokens per GPU, bf16; synthetic
+N(0,1) activations, nn.Linear-initialised weights) and prints ONE JSON line with
+
+* ``value``      tokens/s over all GPUs, inputs resident in HBM, CUDA-event timed;
+* ``e2e``        the same metric through the public call with pinned HOST buffers
+                 (host->device copy of the tokens and device->host read of the result
+                 inside the timed region);
+* ``roofline``   the dominant kernel's achieved TFLOP/s (or GB/s) against the measured peak;
+* ``cpu_baseline`` the CPU oracle (fp32 eager, what the reference executes on a CPU)
+                 timed on this machine's host cores on a bounded sample.
+
+``--impl reference`` times that CPU path alone (rank 0 only).  ``--workload`` selects
+the other benchmark configurations (cfg2 weight-streaming GEMM, cfg3 GEMM + row
+reductions, cfg5 stacked MLP with global reductions).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+import torch.nn as nn  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# DRAM bytes per launch of the dominant kernel, from ncu captures summarised under
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None = not captured yet.
+NCU_TRAFFIC_BYTES = {"cfg4": None, "cfg2": None, "cfg3": None, "cfg5": None}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------------------
+# workloads (same shapes and seeded synthetic inputs as the benchmark definition)
+# --------------------------------------------------------------------------------------
+
+class TransformerMLP(nn.Module):
+    """Linear -> GELU -> Linear -> + residual (the reference's benchmark block,
+    benchmarks/bench_mlp_block.py:160-182)."""
+
+    def __init__(self, d_model, d_intermediate):
+        super().__init__()
+        self.linear1 = nn.Linear(d_model, d_intermediate)
+        self.linear2 = nn.Linear(d_intermediate, d_model)
+
+    def forward(self, x):
+        return self.linear2(F.gelu(self.linear1(x))) + x
+
+
+class Workload:
+    """Resident tensors + one ``step()`` (a pass of the hot path over one batch)."""
+
+    name = ""
+    dtype = "bf16"
+    bound = "tensor"
+
+    def step(self):
+        raise NotImplementedError
+
+    def e2e_step(self):
+        raise NotImplementedError
+
+
+class MLPBlock(Workload):
+    """cfg4 (blocks=1) and cfg5 (blocks=4 + global sum/amax [+ allreduce])."""
+
+    def __init__(self, rows, d_model=4096, d_inter=16384, blocks=1, reductions=False, world=1, seed=0):
+        from fuseml_b200 import kernels as K
+
+        self.K = K
+        self.rows, self.D, self.I, self.blocks, self.reductions, self.world = rows, d_model, d_inter, blocks, reductions, world
+        self.name = "cfg5_stacked_mlp_x4" if blocks > 1 else "cfg4_mlp_block"
+        torch.manual_seed(seed)
+        mods = [TransformerMLP(d_model, d_inter) for _ in range(blocks)]
+        self.params = []
+        for m in mods:
+            self.params.append(tuple(t.detach().to(torch.bfloat16).cuda() for t in
+                                     (m.linear1.weight, m.linear1.bias, m.linear2.weight, m.linear2.bias)))
+        g = torch.Generator().manual_seed(seed + 1 + int(os.environ.get("RANK", "0")))
+        self.x_host = torch.randn(rows, d_model, generator=g).to(torch.bfloat16).pin_memory()
+        self.y_host = torch.empty(rows, d_model, dtype=torch.bfloat16).pin_memory()
+        self.x = self.x_host.cuda()
+        self.h = torch.empty(rows, d_inter, dtype=torch.bfloat16, device="cuda")
+        self.bufs = [torch.empty(rows, d_model, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        self.x_in = torch.empty_like(self.x)
+        self.tokens = rows
+        self.flops_per_launch = 2.0 * rows * d_model * d_inter
+        self.launches_per_step = 2 * blocks + (1 if reductions else 0)
+        self.gemm_launches_per_step = 2 * blocks
+        self.flops = self.flops_per_launch * 2 * blocks
+        # bf16: x read twice + out written, both weights, h written and read back, biases
+        self.algo_bytes = blocks * 2.0 * (3 * rows * d_model + 2 * d_model * d_inter + 2 * rows * d_inter + d_inter + d_model)
+        self.h2d_bytes = rows * d_model * 2
+        self.d2h_bytes = rows * d_model * 2 + (8 if reductions else 0)
+        self.scalars = None
+
+    def _forward(self, x):
+        K = self.K
+        cur = x
+        reds = None
+        for i, (w1, b1, w2, b2) in enumerate(self.params):
+            K.fused_gemm(cur, w1.t(), K.EpilogueProgram().bias(b1).gelu(), out=self.h)
+            out = self.bufs[i % 2]
+            last = self.reductions and i == self.blocks - 1
+            prog = K.EpilogueProgram().bias(b2).add_tensor(cur)
+            if last:
+                _, reds = K.fused_gemm(self.h, w2.t(), prog, out=out, reduce=("sum", "max"), axis=None)
+            else:
+                K.fused_gemm(self.h, w2.t(), prog, out=out)
+            cur = out
+        if reds is not None and self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(reds["sum"], op=dist.ReduceOp.SUM)
+            dist.all_reduce(reds["max"], op=dist.ReduceOp.MAX)
+        self.scalars = reds
+        return cur
+
+    def step(self):
+        return self._forward(self.x)
+
+    def e2e_step(self):
+        self.x_in.copy_(self.x_host, non_blocking=True)
+        y = self._forward(self.x_in)
+        self.y_host.copy_(y, non_blocking=True)
+        if self.scalars is not None:
+            return float(self.scalars["sum"]) + float(self.scalars["max"])  # device->host read of the metrics
+        torch.cuda.current_stream().synchronize()
+        return None
+
+
+class ActHeavyGemm(Workload):
+    """cfg2: out = gelu(h) * sigmoid(h) + r with h = x @ W + b, W row-major [K,N]."""
+
+    name = "cfg2_act_heavy_gemm"
+    bound = "hbm"
+
+    def __init__(self, rows=256, Kd=4096, Nn=16384, seed=0, copies=3):
+        from fuseml_b200 import kernels as K
+
+        self.K = K
+        torch.manual_seed(seed)
+        lin = nn.Linear(Kd, Nn)
+        W = lin.weight.detach().t().contiguous().to(torch.bfloat16).cuda()
+        # rotate several copies of the 128 MB weight so that no launch finds it in the 126 MB L2
+        self.Ws = [W] + [W.clone() for _ in range(copies - 1)]
+        self.b = lin.bias.detach().to(torch.bfloat16).cuda()
+        self.x_host = torch.randn(rows, Kd).to(torch.bfloat16).pin_memory()
+        self.r_host = torch.randn(rows, Nn).to(torch.bfloat16).pin_memory()
+        self.y_host = torch.empty(rows, Nn, dtype=torch.bfloat16).pin_memory()
+        self.x, self.r = self.x_host.cuda(), self.r_host.cuda()
+        self.x_in, self.r_in = torch.empty_like(self.x), torch.empty_like(self.r)
+        self.out = torch.empty(rows, Nn, dtype=torch.bfloat16, device="cuda")
+        self.i = 0
+        self.tokens = rows
+        self.flops_per_launch = self.flops = 2.0 * rows * Kd * Nn
+        self.algo_bytes = 2.0 * (rows * Kd + Kd * Nn + Nn + 2 * rows * Nn)
+        self.launches_per_step = self.gemm_launches_per_step = 1
+        self.h2d_bytes = rows * Kd * 2 + rows * Nn * 2
+        self.d2h_bytes = rows * Nn * 2
+
+    def _forward(self, x, r):
+        K = self.K
+        W = self.Ws[self.i % len(self.Ws)]
+        self.i += 1
+        prog = K.EpilogueProgram().bias(self.b).save().gelu().swap().sigmoid().mul_saved().add_tensor(r)
+        return K.fused_gemm(x, W, prog, out=self.out)
+
+    def step(self):
+        return self._forward(self.x, self.r)
+
+    def e2e_step(self):
+        self.x_in.copy_(self.x_host, non_blocking=True)
+        self.r_in.copy_(self.r_host, non_blocking=True)
+        y = self._forward(self.x_in, self.r_in)
+        self.y_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+
+class GemmRowReduce(Workload):
+    """cfg3: relu(A @ B) -> amax and mean over the last dim; C is never written."""
+
+    name = "cfg3_gemm_row_reductions"
+
+    def __init__(self, rows=8192, Kd=4096, Nn=4096, seed=0):
+        from fuseml_b200 import kernels as K
+
+        self.K = K
+        torch.manual_seed(seed)
+        self.a_host = torch.randn(rows, Kd).to(torch.bfloat16).pin_memory()
+        self.A = self.a_host.cuda()
+        self.A_in = torch.empty_like(self.A)
+        self.B = (torch.randn(Kd, Nn) / Kd ** 0.5).to(torch.bfloat16).cuda()
+        self.out_host = torch.empty(2, rows, dtype=torch.float32).pin_memory()
+        self.tokens = rows
+        self.flops_per_launch = self.flops = 2.0 * rows * Kd * Nn
+        self.algo_bytes = 2.0 * (rows * Kd + Kd * Nn) + 8.0 * rows
+        self.launches_per_step = 2
+        self.gemm_launches_per_step = 1
+        self.h2d_bytes = rows * Kd * 2
+        self.d2h_bytes = rows * 8
+
+    def _forward(self, A):
+        K = self.K
+        _, reds = K.fused_gemm(A, self.B, K.EpilogueProgram().relu(), store=False, reduce=("max", "mean"), axis=-1)
+        return reds
+
+    def step(self):
+        return self._forward(self.A)
+
+    def e2e_step(self):
+        self.A_in.copy_(self.a_host, non_blocking=True)
+        reds = self._forward(self.A_in)
+        self.out_host[0].copy_(reds["max"], non_blocking=True)
+        self.out_host[1].copy_(reds["mean"], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+
+def make_workload(name, world, scaling):
+    if name == "cfg4":
+        rows = 8192 if scaling == "weak" else 8192 // world
+        return MLPBlock(rows, world=world)
+    if name == "cfg5":
+        rows = 32768 // world if scaling == "strong" else 32768 // 8  # 4096 rows per GPU, as at 8 GPUs
+        if world == 1 and scaling == "strong":
+            rows = 32768
+        return MLPBlock(rows, blocks=4, reductions=True, world=world)
+    if name == "cfg2":
+        return ActHeavyGemm()
+    if name == "cfg3":
+        return GemmRowReduce()
+    raise SystemExit(f"unknown workload {name}")
+
+
+# --------------------------------------------------------------------------------------
+# CPU baseline: the oracle's eager fp32 module on the host cores
+# --------------------------------------------------------------------------------------
+
+def cpu_baseline(workload_name, budget_s=20.0, steps=None, sample_rows=None):
+    """Times the CPU oracle (fp32 eager module = what the reference runs on a CPU) on a
+    bounded sample of the workload.  Returns (tokens_per_s, description, cores, ms_per_step, steps)."""
+    from oracle import configs
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    full = dict(configs.FULL[workload_name])
+    default_rows = {"cfg4": 512, "cfg5": 128, "cfg3": 512, "cfg2": 64}[workload_name]
+    rows = sample_rows or default_rows
+    full["M"] = rows
+    case = configs.make(workload_name, sizes=full)
+    with torch.no_grad():
+        case.module(*case.args)  # warm-up
+        times = []
+        t_start = time.perf_counter()
+        n = 0
+        while True:
+            t0 = time.perf_counter()
+            case.module(*case.args)
+            times.append(time.perf_counter() - t0)
+            n += 1
+            if steps is not None:
+                if n >= steps:
+                    break
+            elif time.perf_counter() - t_start > budget_s or n >= 50:
+                break
+    times.sort()
+    med = times[len(times) // 2]
+    desc = (f"{workload_name} at full width, {rows} of the rows per step, fp32 eager PyTorch on "
+            f"{cores} threads, median of {n} steps")
+    return rows / med, desc, cores, med * 1e3, n
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        try:
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        try:
+            rows = [l.strip().split(", ") for l in open(self.path).read().strip().splitlines() if l.strip()]
+            os.unlink(self.path)
+        except Exception:
+            return out
+        sm, reasons, mx, pw = [], set(), None, []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx = float(r[1]); pw.append(float(r[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[3:7]):
+                if v.strip().lower() == "active":
+                    reasons.add(nm)
+        if sm:
+            # median of the upper half: samples taken while the GPU was under load
+            sm.sort()
+            upper = sm[len(sm) // 2:]
+            out.update(sm_mhz=upper[len(upper) // 2], sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(pw) if pw else None)
+        return out
+
+
+# --------------------------------------------------------------------------------------
+
+def run_reference(args):
+    """The reference arm: its CPU path for this workload on the host cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, args.steps)
+    # warm-up passes are part of cpu_baseline(); `steps` timed passes over a bounded sample
+    val, desc, cores, ms, n = cpu_baseline(args.workload, steps=min(steps, 20))
+    line = {
+        "impl": "reference", "metric": "mlp_block_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": n, "warmup": 1, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "CPU path of the reference = eager fp32 module (its compiler returns gm.forward on a CPU)"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg4", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the fused path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from fuseml_b200 import _native, build as _build, kernels as K
+
+    _build.build()
+    _native.load()
+    W = max(3, args.warmup)
+    steps = max(1, args.steps)
+    wl = make_workload(args.workload, world, args.scaling)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        barrier()
+        return float(ms.item())
+
+    for _ in range(W):
+        wl.step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(wl.step, steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    status = K.device_status()
+    if status != 0:
+        raise SystemExit(f"device status {status:#x}: a bounded wait ran out; numbers would be meaningless")
+
+    for _ in range(2):
+        wl.e2e_step()
+    e2e_ms = timed(wl.e2e_step, steps)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_src = load_peaks()
+    ms_per_step = total_ms / steps
+    value = wl.tokens * world / (ms_per_step * 1e-3)
+    launch_ms = ms_per_step / wl.gemm_launches_per_step  # back-to-back launches of the same kernel on one stream
+    if wl.bound == "tensor":
+        achieved = wl.flops_per_launch / (launch_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_kind": f"bf16_tflops_sustained, {peak_src}", "frac_of_burst_peak": achieved / peaks["bf16_tflops"]}
+    else:
+        achieved = wl.algo_bytes / (launch_ms * 1e-3) / 1e9
+        peak = peaks["hbm_gbs"]
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_kind": f"hbm_gbs, {peak_src}"}
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
+    roof["kernel"] = "gemm_epilogue_kernel"
+    roof["launch_us"] = launch_ms * 1e3
+
+    line = {
+        "metric": "mlp_block_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
+        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+        "config": {"workload": wl.name, "rows_per_gpu": wl.tokens, "global_rows": wl.tokens * world,
+                   "l2": "inputs larger than L2 (weights + activations per step exceed 126 MB"
+                         + ("; weight copies rotated)" if args.workload == "cfg2" else ")"),
+                   "parallelism": f"rows sharded over {world} GPU(s), weights replicated"},
+        "e2e": {"value": wl.tokens * world / (e2e_ms / steps * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes, "ms_per_step": e2e_ms / steps},
+        "gpu_launches": wl.launches_per_step * steps,
+        "roofline": roof,
+        "clocks": clocks,
+        "tflops": wl.flops * world / (ms_per_step * 1e-3) / 1e12,
+    }
+    if not args.no_cpu_baseline:
+        try:
+            v, desc, cores, ms, n = cpu_baseline(args.workload, budget_s=15.0)
+            line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
+        except Exception as exc:  # the GPU numbers stand on their own
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": f"failed: {exc!r}"}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -197,7 +197,9 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
 
   const double launch_us = 3.0;
   plan->t_est_us = best + launch_us;
-  if (plan->t_est_us < 2.0 * launch_us) plan->bound = 2;
+  // too few tiles to occupy the machine, or a run time comparable to a launch: neither
+  // roofline applies, the kernel is bound by the latency of one tile's K loop
+  if (plan->t_est_us < 2.0 * launch_us || tiles * 4 < props.sm_count) plan->bound = 2;
   else plan->bound = (plan->t_tensor_us >= plan->t_hbm_us) ? 1 : 0;
   plan->fuse = (v == FUSEML_OK) ? 1 : 0;
   return v;

@@ -1,0 +1,170 @@
+"""The C-ABI library without a GPU: it builds, loads, exports every declared symbol,
+and its host-only entry points (validate / plan / workspace) behave."""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from fuseml_b200 import _native as N
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "fuseml_sm100.h").read_text()
+    return sorted(set(re.findall(r"\b(fuseml_sm100_[a-z_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(native_lib):
+    declared = _declared_symbols()
+    assert len(declared) >= 9
+    for sym in declared:
+        assert hasattr(native_lib, sym), f"{sym} declared in the header but not exported"
+    assert set(declared) == set(N.EXPORTS)
+
+
+def test_abi_version_and_strerror(native_lib):
+    assert native_lib.fuseml_sm100_abi_version() == 1
+    assert N.strerror(0) == "ok"
+    for code in range(1, 13):
+        assert N.strerror(code) and "unknown" not in N.strerror(code)
+    assert "unknown" in N.strerror(999)
+
+
+def _desc(M=8192, Nn=16384, K=4096, ab=N.BF16, kmajor=True):
+    d = N.GemmDesc()
+    d.M, d.N, d.K = M, Nn, K
+    d.a, d.lda = 0x10000, K
+    d.b = 0x20000
+    if kmajor:
+        d.b_stride_k, d.b_stride_n = 1, K
+    else:
+        d.b_stride_k, d.b_stride_n = Nn, 1
+    d.ab_dtype, d.out_dtype = ab, ab
+    d.d, d.ldd = 0x30000, Nn
+    return d
+
+
+def test_validate_accepts_the_benchmark_shapes(native_lib):
+    for (M, Nn, K, km) in [(256, 16384, 4096, False), (8192, 4096, 4096, False), (8192, 16384, 4096, True),
+                           (8192, 4096, 16384, True), (128, 2048, 512, True)]:
+        assert native_lib.fuseml_sm100_validate(C.byref(_desc(M, Nn, K, kmajor=km))) == N.OK
+
+
+def test_validate_rejections(native_lib):
+    v = native_lib.fuseml_sm100_validate
+    assert v(None) == N.E_NULL
+    d = _desc(); d.a = None
+    assert v(C.byref(d)) == N.E_NULL
+    d = _desc(K=0)
+    assert v(C.byref(d)) == N.E_SHAPE
+    d = _desc(); d.ab_dtype = 7
+    assert v(C.byref(d)) == N.E_DTYPE
+    d = _desc(); d.a = 0x10002           # not 16-byte aligned
+    assert v(C.byref(d)) == N.E_LAYOUT
+    d = _desc(K=100); d.lda = 100; d.b_stride_n = 100   # 200-byte rows: not a multiple of 16
+    assert v(C.byref(d)) == N.E_LAYOUT
+    d = _desc(); d.b_stride_k, d.b_stride_n = 3, 5      # no unit stride
+    assert v(C.byref(d)) == N.E_LAYOUT
+    d = _desc(); d.n_ops = 17
+    assert v(C.byref(d)) == N.E_EPILOGUE
+    d = _desc(); d.n_ops = 1; d.ops[0].opcode = 99
+    assert v(C.byref(d)) == N.E_EPILOGUE
+    d = _desc(); d.n_ops = 1; d.ops[0].opcode = N.OP_ADD_T; d.ops[0].slot = 0   # slot without operand
+    assert v(C.byref(d)) == N.E_EPILOGUE
+    d = _desc(); d.d = None               # nothing to produce
+    assert v(C.byref(d)) == N.E_NULL
+    d = _desc(); d.reduce.kinds = N.RED_SUM; d.reduce.axis = N.AXIS_N     # missing output pointer
+    assert v(C.byref(d)) == N.E_NULL
+    d = _desc(); d.reduce.kinds = 64
+    assert v(C.byref(d)) == N.E_REDUCTION
+
+
+def test_fp32_operands_have_no_tma_layout_rule(native_lib):
+    d = _desc(M=128, Nn=2048, K=510, ab=N.F32)
+    d.lda = 510
+    d.b_stride_n = 510
+    assert native_lib.fuseml_sm100_validate(C.byref(d)) == N.OK
+
+
+def _plan(native_lib, d, props=None):
+    p = N.Plan()
+    rc = native_lib.fuseml_sm100_plan(C.byref(d), C.byref(props) if props is not None else None, C.byref(p))
+    return rc, p
+
+
+def test_plan_budgets_and_bounds(native_lib):
+    # compute-bound MLP GEMM: tensor-bound, 256-wide tiles, 4 stages, both TMEM buffers
+    rc, p = _plan(native_lib, _desc(8192, 16384, 4096))
+    assert rc == N.OK and p.fuse == 1
+    assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
+    assert p.stages == 4 and p.tmem_cols == 512 and p.acc_stages == 2
+    assert p.smem_bytes <= 232448
+    assert p.grid == 148 and p.bound == 1
+    assert p.flops == 2.0 * 8192 * 16384 * 4096
+    assert p.t_tensor_us > p.t_hbm_us
+    # weight-streaming shape: HBM-bound
+    rc, p = _plan(native_lib, _desc(256, 16384, 4096, kmajor=False))
+    assert rc == N.OK and p.bound == 0 and p.t_hbm_us > p.t_tensor_us
+    # tiny problem: latency-bound, still fused (single tier: no bypass)
+    rc, p = _plan(native_lib, _desc(128, 512, 2048))
+    assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.grid <= 4 * 2
+
+
+def test_plan_follows_device_props(native_lib):
+    props = N.DeviceProps()
+    native_lib.fuseml_sm100_query(C.byref(props))   # fills B200 defaults when there is no device
+    assert props.sm_count >= 1 and props.tmem_cols == 512
+    props.sm_count = 64
+    rc, p = _plan(native_lib, _desc(8192, 16384, 4096), props)
+    assert rc == N.OK and p.grid == 64
+    props.smem_per_block_optin = 120 * 1024
+    rc, p = _plan(native_lib, _desc(8192, 16384, 4096), props)
+    assert p.stages == 2 and p.smem_bytes <= 120 * 1024
+
+
+def test_plan_reports_unsupported_layout_without_fusing(native_lib):
+    d = _desc(); d.b_stride_k, d.b_stride_n = 3, 5
+    rc, p = _plan(native_lib, d)
+    assert rc == N.E_LAYOUT and p.fuse == 0
+
+
+def test_workspace_bytes(native_lib):
+    w = native_lib.fuseml_sm100_workspace_bytes
+    assert w(C.byref(_desc()), None) == 0
+    d = _desc(8192, 4096, 4096, kmajor=False)
+    d.d = None
+    d.reduce.kinds = N.RED_MAX | N.RED_MEAN
+    d.reduce.axis = N.AXIS_N
+    d.reduce.out_max = 0x40000
+    d.reduce.out_mean = 0x50000
+    # 16 column tiles x 8192 rows x 4 bytes, two partial arrays
+    assert w(C.byref(d), None) == 2 * 16 * 8192 * 4
+    d32 = _desc(128, 2048, 512, ab=N.F32)
+    ld = 3 * 512
+    assert w(C.byref(d32), None) == (128 * ld + 2048 * ld) * 4
+
+
+def test_struct_layout_matches_header():
+    assert C.sizeof(N.EpiOp) == 16
+    assert C.sizeof(N.Operand) == 32
+    assert C.sizeof(N.Reduce) == 48
+    assert C.sizeof(N.GemmDesc) == 656
+    assert C.sizeof(N.Plan) == 88
+    assert C.sizeof(N.DeviceProps) == 40
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    with pytest.raises(N.NativeLibraryError):
+        N.load(tmp_path / "nope.so")
+
+
+def test_cpu_tensors_are_rejected_not_emulated(native_lib):
+    import torch
+    from fuseml_b200.kernels import fused_gemm
+
+    with pytest.raises(RuntimeError):
+        fused_gemm(torch.zeros(128, 64, dtype=torch.bfloat16), torch.zeros(64, 256, dtype=torch.bfloat16))

@@ -1,0 +1,372 @@
+"""GPU parity: the sm_100a kernels (through the C ABI) against the CPU oracle.
+
+Tolerances, from the benchmark definition: bf16 outputs within rtol 1.6e-2 / atol 1e-2
+of the fp32 result, fp32 outputs within 1e-3 / 1e-3, reductions within 1e-3 relative.
+Every test checks the device status word afterwards: a bounded wait that ran out
+would make the launch "succeed" with garbage, and must fail the test instead.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import chain, configs
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = dict(rtol=1.6e-2, atol=1e-2)
+F32_TOL = dict(rtol=1e-3, atol=1e-3)
+
+
+@pytest.fixture(scope="module")
+def K(native_lib):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from fuseml_b200 import kernels
+
+    return kernels
+
+
+def _to_dev(t: torch.Tensor, dtype: str) -> torch.Tensor:
+    td = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    return t.to(td).cuda()
+
+
+def _status_ok(K):
+    assert K.device_status() == 0, "a bounded device-side wait ran out"
+
+
+def _program(K, ops, env):
+    """oracle op tuples -> EpilogueProgram with device tensors."""
+    prog = K.EpilogueProgram()
+    for op in ops:
+        k = op[0]
+        if k in ("bias", "add"):
+            prog.add_tensor(env[op[1]])
+        elif k == "mul":
+            prog.mul_tensor(env[op[1]])
+        elif k == "sub":
+            prog.sub_tensor(env[op[1]])
+        elif k == "rsub":
+            prog.rsub_tensor(env[op[1]])
+        elif k == "add_scalar":
+            prog.add_scalar(op[1])
+        elif k == "mul_scalar":
+            prog.mul_scalar(op[1])
+        elif k == "gelu":
+            prog.gelu()
+        elif k == "gelu_tanh":
+            prog.gelu("tanh")
+        elif k == "store_aux":
+            prog.store_aux(env[op[1]])
+        else:
+            getattr(prog, k)()
+    return prog
+
+
+def run_stages_gpu(K, case) -> dict:
+    """Mirror of oracle.configs.run_stages_oracle on the GPU kernels."""
+    env = {k: _to_dev(v, case.dtype) for k, v in case.tensors.items()}
+    td = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[case.dtype]
+    for st in case.stages:
+        a = env[st.a]
+        b = env[st.b].t() if st.b_view == "t" else env[st.b]
+        prog = _program(K, st.ops, env)
+        res = K.fused_gemm(a, b, prog, out_dtype=td, store=st.out is not None, reduce=st.reduce, axis=st.axis)
+        if st.reduce:
+            out, reds = res
+            for k, nm in st.red_names.items():
+                env[nm] = reds[k]
+        else:
+            out = res
+        if st.out is not None:
+            env[st.out] = out
+    torch.cuda.synchronize()
+    return {k: env[k].float().cpu().numpy() for k in case.outputs}
+
+
+def _assert_close(got, ref, dtype, what):
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape, what
+    if ref.ndim <= 1:
+        scale = max(np.abs(ref).max(), 1e-30)
+        assert np.abs(got - ref).max() <= 1e-3 * scale + 1e-6, what
+    else:
+        np.testing.assert_allclose(got, ref, err_msg=what, **(F32_TOL if dtype == "f32" else BF16_TOL))
+
+
+# ---- the five configurations, scaled down, against oracle and golden fixtures ----
+
+@pytest.mark.parametrize("name", list(configs.MAKERS))
+def test_config_small_matches_oracle_and_reference_fixture(K, golden_dir, name):
+    case = configs.make(name, small=(name != "cfg1"))
+    got = run_stages_gpu(K, case)
+    _status_ok(K)
+    oracle = configs.run_stages_oracle(case)
+    golden = np.load(golden_dir / f"numeric_{name}.npz")
+    for k in case.outputs:
+        # against the stage oracle (same bf16 storage points): tight
+        if np.asarray(oracle[k]).ndim <= 1:
+            _assert_close(got[k], oracle[k], case.dtype, f"{name}:{k} vs oracle")
+        else:
+            tol = F32_TOL if case.dtype == "f32" else dict(rtol=1.6e-2, atol=1e-2)
+            np.testing.assert_allclose(got[k], oracle[k], err_msg=f"{name}:{k} vs oracle", **tol)
+        # against the reference's own output (fp32 eager on the same inputs)
+        if name == "cfg5" and k == "amax":
+            np.testing.assert_allclose(got[k], golden[k], **BF16_TOL)
+        else:
+            _assert_close(got[k], golden[k], case.dtype, f"{name}:{k} vs reference fixture")
+
+
+# ---- shape / layout sweep -------------------------------------------------------
+
+SHAPES = [
+    (1, 8, 8), (7, 24, 40), (128, 64, 256), (128, 512, 256), (129, 72, 264), (200, 136, 304),
+    (384, 256, 640), (512, 512, 1024), (1000, 1000, 1000), (2048, 1024, 4096), (300, 4104, 520),
+]
+
+
+@pytest.mark.parametrize("b_view", ["t", "n"])
+@pytest.mark.parametrize("M,Kd,Nn", SHAPES)
+def test_plain_gemm_bf16(K, M, Kd, Nn, b_view):
+    g = torch.Generator().manual_seed(M * 7 + Kd * 3 + Nn)
+    a = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
+    b = (torch.randn(Kd, Nn, generator=g) / Kd ** 0.5).to(torch.bfloat16)
+    ref = chain.fused_chain(a.float().numpy(), b.float().numpy(), (), out_dtype="bf16")["d"]
+    bd = b.cuda() if b_view == "n" else b.t().contiguous().cuda().t()
+    out = K.fused_gemm(a.cuda(), bd)
+    torch.cuda.synchronize()
+    _status_ok(K)
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, **BF16_TOL)
+
+
+@pytest.mark.parametrize("dtype,tol", [("f16", dict(rtol=2e-3, atol=2e-3)), ("f32", dict(rtol=1e-4, atol=1e-4))])
+@pytest.mark.parametrize("b_view", ["t", "n"])
+def test_other_operand_dtypes(K, dtype, tol, b_view):
+    td = {"f16": torch.float16, "f32": torch.float32}[dtype]
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(200, 136, generator=g).to(td)
+    b = (torch.randn(136, 304, generator=g) / 12).to(td)
+    ref = chain.fused_chain(a.float().numpy(), b.float().numpy(), (), out_dtype=dtype)["d"]
+    bd = b.cuda() if b_view == "n" else b.t().contiguous().cuda().t()
+    out = K.fused_gemm(a.cuda(), bd)
+    torch.cuda.synchronize()
+    _status_ok(K)
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, **tol)
+
+
+def test_fp32_is_close_to_true_fp32_not_tf32(K):
+    """fp32 operands run as three TF32 products; the result must be far better than one."""
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(128, 2048, generator=g)
+    b = torch.randn(2048, 512, generator=g) / 45
+    ref = a.double() @ b.double()
+    out = K.fused_gemm(a.cuda(), b.cuda()).cpu().double()
+    _status_ok(K)
+    err = (out - ref).abs().max().item()
+    assert err < 2e-5, err      # a single TF32 pass gives ~1e-3 here
+
+
+def test_both_tile_widths(K):
+    import ctypes as C
+
+    from fuseml_b200 import _native as N
+
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(384, 256, generator=g).to(torch.bfloat16).cuda()
+    b = (torch.randn(256, 640, generator=g) / 16).to(torch.bfloat16).cuda()
+    ref = (a.float() @ b.float()).cpu().numpy()
+    for tile_n in (128, 256):
+        out = torch.empty(384, 640, dtype=torch.bfloat16, device="cuda")
+        desc = N.GemmDesc()
+        K.fill_desc(desc, a, b, None, out, torch.bfloat16)
+        plan = K.plan_for(desc, K.device_props())
+        plan.tile_n = tile_n
+        plan.grid = 5
+        K.fused_gemm(a, b, None, out=out, plan=plan)
+        torch.cuda.synchronize()
+        _status_ok(K)
+        np.testing.assert_allclose(out.float().cpu().numpy(), ref, **BF16_TOL)
+
+
+def test_strided_views_without_copies(K):
+    """Row-strided A, row-strided output and a column-sliced weight are addressed in place."""
+    g = torch.Generator().manual_seed(4)
+    big_a = torch.randn(256, 512, generator=g).to(torch.bfloat16).cuda()
+    a = big_a[:, :256]                      # lda = 512
+    w = (torch.randn(384, 512, generator=g) / 16).to(torch.bfloat16).cuda()
+    b = w[:, 128:384].t()                   # [256, 384] view, K-major with ld 512, offset 256 bytes
+    big_out = torch.zeros(256, 1024, dtype=torch.bfloat16, device="cuda")
+    out = big_out[:, 512:896]               # ldd = 1024
+    K.fused_gemm(a, b, None, out=out)
+    torch.cuda.synchronize()
+    _status_ok(K)
+    ref = a.float() @ b.float()
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
+    assert float(big_out[:, :512].abs().max()) == 0.0 and float(big_out[:, 896:].abs().max()) == 0.0
+
+
+def test_unsupported_layout_raises(K):
+    a = torch.zeros(64, 100, dtype=torch.bfloat16, device="cuda")   # 200-byte rows
+    b = torch.zeros(100, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="layout"):
+        K.fused_gemm(a, b)
+
+
+# ---- epilogue programs ----------------------------------------------------------------
+
+def _epi_case(K, ops_fn, M=200, Kd=136, Nn=304, dtype="bf16", seed=0, **kw):
+    g = torch.Generator().manual_seed(seed)
+    td = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    a = torch.randn(M, Kd, generator=g).to(td)
+    b = (torch.randn(Kd, Nn, generator=g) / Kd ** 0.5).to(td)
+    T = {
+        "row": torch.randn(Nn, generator=g).to(td), "col": torch.randn(M, 1, generator=g).to(td),
+        "full": torch.randn(M, Nn, generator=g).to(td), "full32": torch.randn(M, Nn, generator=g),
+        "row2d": torch.randn(1, Nn, generator=g).to(td), "vecm": torch.randn(M, generator=g).to(td),
+    }
+    ops = ops_fn()
+    np_ops = [tuple(T[o].float().numpy() if isinstance(o, str) and i > 0 else o for i, o in enumerate(op)) for op in ops]
+    ref = chain.fused_chain(a.float().numpy(), b.float().numpy(), np_ops, out_dtype=dtype, **kw)
+    env = {k: v.cuda() for k, v in T.items()}
+    prog = _program(K, ops, env)
+    res = K.fused_gemm(a.cuda(), b.cuda(), prog, **{("reduce" if k == "reduce" else k): v for k, v in kw.items()})
+    torch.cuda.synchronize()
+    _status_ok(K)
+    return res, ref
+
+
+EPILOGUES = {
+    "relu": lambda: [("relu",)],
+    "bias_gelu": lambda: [("bias", "row"), ("gelu",)],
+    "bias_gelu_tanh": lambda: [("bias", "row"), ("gelu_tanh",)],
+    "bias_sigmoid": lambda: [("bias", "row"), ("sigmoid",)],
+    "bias_residual": lambda: [("bias", "row"), ("add", "full")],
+    "residual_fp32_operand": lambda: [("add", "full32")],
+    "scalars": lambda: [("mul_scalar", 0.5), ("add_scalar", 0.125)],
+    "col_vector": lambda: [("mul", "col")],
+    "row_2d": lambda: [("add", "row2d")],
+    "sub_rsub": lambda: [("sub", "row"), ("rsub", "full")],
+    "dag_gelu_mul_sigmoid_add": lambda: [("bias", "row"), ("save",), ("gelu",), ("swap",), ("sigmoid",),
+                                         ("mul_saved",), ("add", "full")],
+    "dag_add_saved": lambda: [("save",), ("relu",), ("add_saved",)],
+    "long_chain": lambda: [("bias", "row"), ("relu",), ("mul_scalar", 2.0), ("add", "full"), ("sigmoid",),
+                           ("mul", "col"), ("add_scalar", -0.25), ("gelu",)],
+}
+
+
+@pytest.mark.parametrize("name", list(EPILOGUES))
+def test_epilogue_program(K, name):
+    out, ref = _epi_case(K, EPILOGUES[name])
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref["d"], **BF16_TOL)
+
+
+def test_one_d_operand_of_length_m_runs_along_rows(K):
+    # square-ish case where the 1-D length equals M but not N
+    out, ref = _epi_case(K, lambda: [("add", "vecm")], M=200, Nn=304)
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref["d"], **BF16_TOL)
+
+
+def test_epilogue_fp32_and_fp16_outputs(K):
+    out, ref = _epi_case(K, EPILOGUES["bias_gelu"], dtype="f32")
+    np.testing.assert_allclose(out.cpu().numpy(), ref["d"], **F32_TOL)
+    out, ref = _epi_case(K, lambda: [("mul_scalar", 1e5)], dtype="f16")   # saturates at 65504
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all() and np.abs(got).max() == 65504.0
+    np.testing.assert_allclose(got, ref["d"], rtol=2e-3, atol=1.0)
+
+
+def test_escape_store_of_an_intermediate(K):
+    g = torch.Generator().manual_seed(9)
+    a = torch.randn(200, 136, generator=g).to(torch.bfloat16)
+    b = (torch.randn(136, 304, generator=g) / 12).to(torch.bfloat16)
+    aux = torch.zeros(200, 304, dtype=torch.bfloat16, device="cuda")
+    prog = K.EpilogueProgram().relu().store_aux(aux).mul_scalar(3.0)
+    out = K.fused_gemm(a.cuda(), b.cuda(), prog)
+    torch.cuda.synchronize()
+    _status_ok(K)
+    ref = chain.fused_chain(a.float().numpy(), b.float().numpy(), [("relu",), ("store_aux",), ("mul_scalar", 3.0)])
+    np.testing.assert_allclose(aux.float().cpu().numpy(), ref["aux"][0], **BF16_TOL)
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref["d"], **BF16_TOL)
+
+
+# ---- reductions ----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("axis", [-1, 0, None])
+@pytest.mark.parametrize("store", [False, True])
+def test_fused_reductions(K, axis, store):
+    (out, reds), ref = _epi_case(K, EPILOGUES["bias_gelu"], M=520, Kd=256, Nn=1000, store=store,
+                                 reduce=("sum", "max", "mean"), axis=axis)
+    if store:
+        np.testing.assert_allclose(out.float().cpu().numpy(), ref["d"], **BF16_TOL)
+    else:
+        assert out is None
+    for k in ("sum", "max", "mean"):
+        _assert_close(reds[k].cpu().numpy(), ref[k], "bf16", f"{k} axis={axis}")
+
+
+def test_reduction_of_negative_values_and_ragged_edges(K):
+    """max must not be polluted by the zero padding of edge tiles."""
+    (out, reds), ref = _epi_case(K, lambda: [("add_scalar", -50.0)], M=130, Kd=72, Nn=260, store=False,
+                                 reduce=("max", "sum"), axis=-1)
+    assert (reds["max"].cpu().numpy() < -30).all()
+    _assert_close(reds["max"].cpu().numpy(), ref["max"], "bf16", "max")
+    _assert_close(reds["sum"].cpu().numpy(), ref["sum"], "bf16", "sum")
+
+
+@pytest.mark.parametrize("axis", [-1, 0, None])
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_standalone_reduce_tail(K, axis, dtype):
+    g = torch.Generator().manual_seed(2)
+    td = {"bf16": torch.bfloat16, "f32": torch.float32}[dtype]
+    x = torch.randn(1000, 3001 if dtype == "f32" else 3000, generator=g).to(td)
+    r = K.reduce_tail(x.cuda(), ("sum", "max", "mean"), axis=axis)
+    torch.cuda.synchronize()
+    ref = chain.reduce_tail(x.float().numpy(), ("sum", "max", "mean"), axis)
+    for k in ("sum", "max", "mean"):
+        got = r[k].cpu().numpy()
+        scale = max(np.abs(ref[k]).max(), 1.0)
+        assert np.abs(got.astype(np.float64) - ref[k]).max() <= 1e-3 * scale, (k, axis)
+
+
+# ---- full-size properties (no CPU oracle at these sizes) --------------------------------
+
+def test_full_size_linearity_and_checksum(K):
+    """At the benchmark's GEMM size: the kernel is linear in A (exactly, for power-of-two
+    scaling) and a column checksum agrees with a GEMV computed independently."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    M, Kd, Nn = 8192, 4096, 4096
+    a = torch.randn(M, Kd, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(Nn, Kd, generator=g, device="cuda") / 64).to(torch.bfloat16)
+    out1 = K.fused_gemm(a, w.t(), out_dtype=torch.float32)
+    out2 = K.fused_gemm(a * 2, w.t(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    _status_ok(K)
+    assert torch.equal(out2, out1 * 2)
+    # checksum of checksums: (1^T A) W^T == 1^T (A W^T)
+    col = (a.double().sum(0) @ w.double().t())
+    got = out1.double().sum(0)
+    rel = ((got - col).abs().max() / col.abs().max()).item()
+    assert rel < 1e-4, rel
+
+
+def test_full_size_cfg3_reductions_match_unfused_path(K):
+    """relu(A@B) -> amax/mean fused (C never stored) equals storing C in fp32 and reducing it."""
+    case = configs.make("cfg3")
+    A = case.tensors["A"].to(torch.bfloat16).cuda()
+    B = case.tensors["B"].to(torch.bfloat16).cuda()
+    prog = K.EpilogueProgram().relu()
+    _, reds = K.fused_gemm(A, B, prog, store=False, reduce=("max", "mean"), axis=-1)
+    c = K.fused_gemm(A, B, K.EpilogueProgram().relu(), out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    _status_ok(K)
+    assert torch.equal(reds["max"], c.amax(-1))
+    ref_mean = c.double().mean(-1)
+    assert ((reds["mean"].double() - ref_mean).abs().max() / ref_mean.abs().max()).item() < 1e-5
+    # and against the fp32 eager path of the oracle on a slice of rows (CPU time bounded)
+    rows = slice(0, 256)
+    e = torch.relu(case.tensors["A"][rows] @ case.tensors["B"])
+    _assert_close(reds["max"][rows].cpu().numpy(), e.amax(-1).numpy(), "bf16", "amax vs eager")
+    _assert_close(reds["mean"][rows].cpu().numpy(), e.double().mean(-1).float().numpy(), "bf16", "mean vs eager")
