@@ -312,7 +312,7 @@ def test_fused_reductions(K, axis, store):
 
 def test_reduction_of_negative_values_and_ragged_edges(K):
     """max must not be polluted by the zero padding of edge tiles."""
-    (out, reds), ref = _epi_case(K, lambda: [("add_scalar", -50.0)], M=130, Kd=72, Nn=260, store=False,
+    (out, reds), ref = _epi_case(K, lambda: [("add_scalar", -50.0)], M=130, Kd=72, Nn=264, store=False,
                                  reduce=("max", "sum"), axis=-1)
     assert (reds["max"].cpu().numpy() < -30).all()
     _assert_close(reds["max"].cpu().numpy(), ref["max"], "bf16", "max")
