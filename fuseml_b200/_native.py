@@ -94,6 +94,7 @@ EXPORTS = (
     "fuseml_sm100_query", "fuseml_sm100_plan", "fuseml_sm100_workspace_bytes", "fuseml_sm100_validate",
     "fuseml_sm100_gemm_epilogue", "fuseml_sm100_reduce_tail", "fuseml_sm100_device_status",
     "fuseml_sm100_strerror", "fuseml_sm100_abi_version",
+    "fuseml_sm100_gemm_epilogue_noalloc", "fuseml_sm100_noalloc_scratch_bytes",
 )
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfuseml_sm100.so"
@@ -121,6 +122,10 @@ def _declare(lib: C.CDLL) -> None:
     lib.fuseml_sm100_validate.argtypes = [C.POINTER(GemmDesc)]
     lib.fuseml_sm100_gemm_epilogue.restype = C.c_int
     lib.fuseml_sm100_gemm_epilogue.argtypes = [C.POINTER(GemmDesc), C.POINTER(Plan), C.c_void_p]
+    lib.fuseml_sm100_gemm_epilogue_noalloc.restype = C.c_int
+    lib.fuseml_sm100_gemm_epilogue_noalloc.argtypes = [C.POINTER(GemmDesc), C.POINTER(Plan), C.c_void_p]
+    lib.fuseml_sm100_noalloc_scratch_bytes.restype = C.c_int64
+    lib.fuseml_sm100_noalloc_scratch_bytes.argtypes = []
     lib.fuseml_sm100_reduce_tail.restype = C.c_int
     lib.fuseml_sm100_reduce_tail.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                              C.POINTER(Reduce), C.c_void_p]

@@ -335,6 +335,81 @@ int fuseml_sm100_reduce_tail(const void* x, int32_t dtype, int64_t M, int64_t N,
   return run_finalize(*r, w, ws, count, stream);
 }
 
+// ---------------------------------------------------------------------------------
+// Entry point for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the moment they need a fused
+// GEMM with a reduction tail: code running inside another framework's memory pool
+// with the allocator locked, a plugin that was handed a fixed memory budget at load
+// time, or a latency-critical serving loop where an allocation (and the implicit
+// synchronisation it can cause) is not acceptable.  For them the reduction partials
+// live in the fixed array below instead of a caller-provided workspace.
+//
+// Cost and limits: every GPU that loads this library holds kNoAllocScratchBytes
+// (8 MiB) of device memory until the process exits, whether or not this entry point
+// is ever called.  A launch whose scratch need is larger is rejected with
+// FUSEML_E_LIMIT.  The array is shared by every call: it keeps whatever the last
+// call left there (the kernels overwrite every slot they later read, so nothing has
+// to be cleared), and two calls whose kernels overlap on the GPU (different streams,
+// or different host threads) race on it - serialise them on one stream.
+// ---------------------------------------------------------------------------------
+namespace fuseml {
+constexpr int64_t kNoAllocScratchBytes = 8ll << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_noalloc_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device.  `g_noalloc_scratch` in
+// host code is only a handle for the symbol, not an address a kernel can use; the real
+// address differs per device and is looked up once per device, with that device
+// current, and cached.
+static int noalloc_scratch_address(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
+  if (dev < 0 || dev >= kMaxDevices) return FUSEML_E_DEVICE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return FUSEML_E_DEVICE;
+    }
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return FUSEML_OK;
+}
+}  // namespace fuseml
+
+int64_t fuseml_sm100_noalloc_scratch_bytes(void) { return kNoAllocScratchBytes; }
+
+int fuseml_sm100_gemm_epilogue_noalloc(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan_in,
+                                       void* cuda_stream) {
+  int rc = validate_desc(desc);
+  if (rc != FUSEML_OK) return rc;
+  fuseml_plan_t plan;
+  if (plan_in != nullptr) {
+    plan = *plan_in;
+  } else {
+    fuseml_device_props_t props;
+    if (fuseml_sm100_query(&props) != FUSEML_OK) return FUSEML_E_DEVICE;
+    rc = make_plan(desc, &props, &plan);
+    if (rc != FUSEML_OK) return rc;
+  }
+  WorkspaceLayout w;
+  workspace_layout(desc, &plan, &w);
+  if (w.total > kNoAllocScratchBytes) return FUSEML_E_LIMIT;
+  void* scratch = nullptr;
+  rc = noalloc_scratch_address(&scratch);
+  if (rc != FUSEML_OK) return rc;
+  fuseml_gemm_desc_t local = *desc;       // the caller's descriptor is left untouched
+  local.reduce.workspace = scratch;
+  local.reduce.workspace_bytes = kNoAllocScratchBytes;
+  return fuseml_sm100_gemm_epilogue(&local, &plan, cuda_stream);
+}
+
 int fuseml_sm100_device_status(void* cuda_stream, int32_t* status_out) {
   if (status_out == nullptr) return FUSEML_E_NULL;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);

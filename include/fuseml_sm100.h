@@ -212,6 +212,23 @@ int fuseml_sm100_validate(const fuseml_gemm_desc_t* desc);
 int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan,
                                void* cuda_stream);
 
+/* No counterpart in the reference.  Same contract as fuseml_sm100_gemm_epilogue, for
+ * callers that cannot allocate device memory when they launch (code running under
+ * another framework's locked memory pool, plugins with a fixed memory budget,
+ * allocation-free serving loops): reduction partials and the fp32 operand expansion
+ * use a fixed scratch array inside the library instead of desc->reduce.workspace
+ * (which is ignored).  The call allocates and frees nothing.
+ *   - Limit: the launch may need at most fuseml_sm100_noalloc_scratch_bytes() (8 MiB)
+ *     of scratch; more returns FUSEML_E_LIMIT.  Each GPU that loads the library holds
+ *     those 8 MiB until the process exits.
+ *   - The first call on each device looks up the array's device address; make that
+ *     first call before starting any stream capture on that device.
+ *   - All calls share the one array: calls that can overlap on the GPU (other
+ *     streams, other threads) race on it; keep them on one stream. */
+int fuseml_sm100_gemm_epilogue_noalloc(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan,
+                                       void* cuda_stream);
+int64_t fuseml_sm100_noalloc_scratch_bytes(void);
+
 /* Stand-alone reduction tail over an existing [M,N] matrix (used when the
  * reduction cannot be absorbed into the producing GEMM): sum / max / mean
  * over rows, columns or everything; fp32 results.  Replaces the eager
