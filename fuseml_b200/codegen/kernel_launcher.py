@@ -1,0 +1,278 @@
+"""Runtime dispatch of one fused chain: live tensors in, C-ABI launch on the current stream.
+
+Counterpart of the reference's ``KernelLauncher`` (fuseml/codegen/kernel_launcher.py:309-847).
+The call contract is unchanged — ``launcher(*input_tensors)`` with tensors in
+``FusionGroup.inputs`` order, ``__name__ == "fuseml_fused_kernel"`` for FX node naming,
+``ValueError`` on arity / unknown operand names, outputs allocated through torch per call,
+no host synchronisation — but there is no Triton kernel object any more: ``kernel_fn`` is a
+:class:`~fuseml_b200.codegen.kernel_generator.KernelSpec`, and the launch is
+``fuseml_sm100_gemm_epilogue`` through ``ctypes``.
+
+Per distinct (shape, stride) signature of the inputs the launcher keeps one prepared
+descriptor, the plan the roofline router returned for it and a workspace per stream; a
+call then only writes pointers into the descriptor.  Groups with several outputs
+(escape stores, extra reductions) return a tuple ``(primary, *escapes, *reductions)``,
+which is what graph surgery's ``getitem`` nodes index.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Any, Callable, Sequence
+
+import torch
+
+from .. import _native as N
+from .. import kernels as K
+from .._logging import logger
+from .kernel_generator import KernelSpec, TensorDescriptor
+
+_DEFAULT_BLOCK_SIZE_M = 128
+_DEFAULT_BLOCK_SIZE_N = 256
+_DEFAULT_BLOCK_SIZE_K = 64
+_DEFAULT_GROUP_SIZE_M = 8
+
+_RED_BIT = {"sum": N.RED_SUM, "max": N.RED_MAX, "mean": N.RED_MEAN}
+_RED_FIELD = {"sum": "out_sum", "max": "out_max", "mean": "out_mean"}
+_AXIS_CODE = {0: N.AXIS_M, 1: N.AXIS_N, 2: N.AXIS_ALL}
+
+
+@dataclass(frozen=True)
+class LaunchParams:
+    """Frozen launch configuration: the tile the CTA computes, the K extent of one
+    shared-memory stage, the rasterisation group, epilogue warps and ring depth.
+    (The reference froze Triton ``BLOCK_SIZE_*`` / ``num_warps`` / ``num_stages`` here,
+    fuseml/codegen/kernel_launcher.py:99-127.)"""
+    block_m: int
+    block_n: int
+    block_k: int
+    group_size_m: int
+    num_warps: int
+    num_stages: int
+
+
+def compute_launch_params(M: int, Ncols: int, Kd: int, dtype: torch.dtype = torch.bfloat16, *,
+                          block_size_m: int = _DEFAULT_BLOCK_SIZE_M, block_size_n: int = _DEFAULT_BLOCK_SIZE_N,
+                          block_size_k: int = _DEFAULT_BLOCK_SIZE_K, group_size_m: int = _DEFAULT_GROUP_SIZE_M,
+                          sram_autotuner: Any = None) -> LaunchParams:
+    """Ask the native router (host only, no GPU needed) for the tile shape of an M x N x K problem."""
+    desc = N.GemmDesc()
+    desc.M, desc.N, desc.K = int(M), int(Ncols), int(Kd)
+    desc.a, desc.b, desc.d = 0x1000, 0x2000, 0x3000          # layout-only query: aligned dummies
+    desc.lda, desc.b_stride_k, desc.b_stride_n, desc.ldd = int(Kd), 1, int(Kd), int(Ncols)
+    code = K.dtype_code(dtype)
+    desc.ab_dtype = desc.out_dtype = code
+    if code != N.F32 and (Kd * 2) % 16 != 0:
+        desc.lda = desc.b_stride_n = (int(Kd) + 7) // 8 * 8
+    plan = N.Plan()
+    rc = N.load().fuseml_sm100_plan(C.byref(desc), None, C.byref(plan))
+    if rc != N.OK:
+        return LaunchParams(block_size_m, block_size_n, block_size_k, group_size_m, 6, 4)
+    return LaunchParams(plan.tile_m, plan.tile_n, plan.tile_k, plan.group_m, 6, plan.stages)
+
+
+class _Prepared:
+    """One (shape, stride) signature: filled descriptor, plan, workspace size, output shapes."""
+    __slots__ = ("desc", "plan", "ws_bytes", "ws", "M", "N", "K", "red_len", "left", "right")
+
+
+class KernelLauncher:
+    _POST_KERNEL_NOOP = 0
+    _POST_KERNEL_CAST_ONLY = 1
+
+    def __init__(self, kernel_fn: KernelSpec, input_descriptors: Sequence[TensorDescriptor],
+                 output_descriptor: TensorDescriptor, intermediate_descriptors: Sequence[TensorDescriptor],
+                 left_name: str, right_name: str, launch_params: LaunchParams | None = None,
+                 block_size_m: int = _DEFAULT_BLOCK_SIZE_M, block_size_n: int = _DEFAULT_BLOCK_SIZE_N,
+                 block_size_k: int = _DEFAULT_BLOCK_SIZE_K, group_size_m: int = _DEFAULT_GROUP_SIZE_M,
+                 reduction_op: str | None = None, reduction_axis: int | None = None,
+                 eager_fn: Callable | None = None, is_autotuned: bool = False, sram_autotuner: Any = None,
+                 mean_epilogue_fused: bool = True, reduction_dtypes: Sequence[torch.dtype] | None = None) -> None:
+        self.__name__ = "fuseml_fused_kernel"
+        if not isinstance(kernel_fn, KernelSpec):
+            raise TypeError("kernel_fn must be a KernelSpec (the lowered form of a FusionGroup)")
+        self._spec = kernel_fn
+        self._kernel_fn = kernel_fn
+        self._input_descriptors = list(input_descriptors)
+        self._output_descriptor = output_descriptor
+        self._intermediate_descriptors = list(intermediate_descriptors)
+        names = [d.name for d in self._input_descriptors]
+        for label, name in (("left_name", left_name), ("right_name", right_name)):
+            if name not in names:
+                raise ValueError(f"{label}={name!r} not found in input_descriptors: {names}")
+        self._left_idx = names.index(left_name)
+        self._right_idx = names.index(right_name)
+        if (self._left_idx, self._right_idx) != (kernel_fn.left_index, kernel_fn.right_index):
+            raise ValueError("left/right operand names disagree with the kernel specification")
+        # reductions: from the spec; the reduction_op / reduction_axis keywords describe the
+        # classic single-reduction case and are checked against it
+        self._reductions = list(kernel_fn.reductions)
+        if reduction_op is not None and not self._reductions:
+            raise ValueError(f"reduction_op={reduction_op!r} given but the kernel has no reduction")
+        self._reduction_op = reduction_op or (self._reductions[0].op if self._reductions else None)
+        self._reduction_axis = reduction_axis if reduction_axis is not None else (
+            self._reductions[0].axis if self._reductions else 1)
+        self._is_reduced = bool(self._reductions) and not kernel_fn.store_output and not intermediate_descriptors
+        self._reduction_dtypes = list(reduction_dtypes) if reduction_dtypes is not None else \
+            [output_descriptor.dtype] * len(self._reductions)
+        self._launch_params = launch_params
+        self._is_autotuned = is_autotuned
+        self._sram_autotuner = sram_autotuner
+        self._skip_stride_check = all(all(s >= 0 for s in d.stride) for d in self._input_descriptors)
+        self._prepared: dict[tuple, _Prepared] = {}
+        self._lib = None
+        self.launch_count = 0
+        # operand slots of the program: input indices in order of first use
+        self._slot_inputs: list[int] = []
+        self._aux_slots: dict[int, int] = {}
+        for st in kernel_fn.steps:
+            if st.opcode == N.OP_STORE_AUX:
+                continue
+            if st.input_index >= 0 and st.input_index not in self._slot_inputs:
+                self._slot_inputs.append(st.input_index)
+        n_in = len(self._slot_inputs)
+        for st in kernel_fn.steps:
+            if st.opcode == N.OP_STORE_AUX and st.aux_index not in self._aux_slots:
+                self._aux_slots[st.aux_index] = n_in + len(self._aux_slots)
+        if n_in + len(self._aux_slots) > N.MAX_OPERANDS:
+            raise ValueError(f"chain needs more than {N.MAX_OPERANDS} operand slots")
+
+    # ------------------------------------------------------------------ helpers
+    @staticmethod
+    def _has_negative_strides(t: torch.Tensor) -> bool:
+        return any(s < 0 for s in t.stride())
+
+    @staticmethod
+    def _materialize_if_needed(t: torch.Tensor) -> torch.Tensor:
+        return t.contiguous() if any(s < 0 for s in t.stride()) else t
+
+    def _prepare(self, inputs: Sequence[torch.Tensor], key: tuple) -> _Prepared:
+        spec = self._spec
+        left, right = inputs[self._left_idx], inputs[self._right_idx]
+        if left.dim() != 2 or right.dim() != 2:
+            raise N.NativeLibraryError("fused GEMM operands must be 2-D")
+        prog = K.EpilogueProgram()
+        slot_tensors = [inputs[i] for i in self._slot_inputs]
+        prog.operands = list(slot_tensors)
+        for st in spec.steps:
+            if st.opcode == N.OP_STORE_AUX:
+                prog.ops.append((st.opcode, self._aux_slots[st.aux_index], 0.0))
+            elif st.input_index >= 0:
+                prog.ops.append((st.opcode, self._slot_inputs.index(st.input_index), 0.0))
+            else:
+                prog.ops.append((st.opcode, 0, st.imm))
+        p = _Prepared()
+        p.desc = N.GemmDesc()
+        out_dtype = self._output_descriptor.dtype if spec.store_output else left.dtype
+        M, Ncols, Kd = K.fill_desc(p.desc, left, right, prog, None, out_dtype)
+        p.left, p.right = p.desc._keepalive
+        p.M, p.N, p.K = M, Ncols, Kd
+        # aux (escape-store) operands: row-major [M, N], pointer filled per call
+        for aux_index, slot in self._aux_slots.items():
+            d = self._intermediate_descriptors[aux_index]
+            o = p.desc.operands[slot]
+            o.stride_m, o.stride_n, o.dtype = Ncols, 1, K.dtype_code(d.dtype)
+            o.ptr = 0x1000
+        p.desc.n_operands = len(self._slot_inputs) + len(self._aux_slots)
+        if spec.store_output:
+            p.desc.d, p.desc.ldd = 0x1000, Ncols      # placeholder pointer for validation / planning
+        p.red_len = 0
+        if self._reductions:
+            kinds = 0
+            for r in self._reductions:
+                kinds |= _RED_BIT[r.op]
+                setattr(p.desc.reduce, _RED_FIELD[r.op], 0x1000)
+            axis = self._reductions[0].axis
+            p.desc.reduce.kinds = kinds
+            p.desc.reduce.axis = _AXIS_CODE[axis]
+            p.red_len = M if axis == 1 else (Ncols if axis == 0 else 1)
+        p.plan = K.plan_for(p.desc, K.device_props(left.device))
+        if self._launch_params is not None and not self._is_autotuned and self._launch_params.block_n in (128, 256):
+            if self._launch_params.block_n != p.plan.tile_n:
+                p.plan.tile_n = self._launch_params.block_n
+                tiles = ((M + 127) // 128) * ((Ncols + p.plan.tile_n - 1) // p.plan.tile_n)
+                p.plan.grid = max(1, min(p.plan.grid if p.plan.grid > 0 else tiles, tiles))
+        p.ws_bytes = int(self._lib.fuseml_sm100_workspace_bytes(C.byref(p.desc), C.byref(p.plan)))
+        if p.ws_bytes < 0:
+            raise N.NativeLibraryError("fuseml_sm100_workspace_bytes rejected the descriptor")
+        p.ws = {}
+        self._prepared[key] = p
+        logger.debug("prepared launch M=%d N=%d K=%d tile_n=%d grid=%d ws=%d B", M, Ncols, Kd,
+                     p.plan.tile_n, p.plan.grid, p.ws_bytes)
+        return p
+
+    # ------------------------------------------------------------------ hot path
+    def __call__(self, *input_tensors: torch.Tensor):
+        if len(input_tensors) != len(self._input_descriptors):
+            raise ValueError(f"Expected {len(self._input_descriptors)} input tensor(s), got {len(input_tensors)}.")
+        if not self._skip_stride_check:
+            input_tensors = tuple(self._materialize_if_needed(t) for t in input_tensors)
+        if self._lib is None:
+            self._lib = N.load()
+        key = tuple((t.shape, t.stride()) for t in input_tensors)
+        p = self._prepared.get(key)
+        if p is None:
+            p = self._prepare(input_tensors, key)
+        spec = self._spec
+        desc = p.desc
+        left, right = input_tensors[self._left_idx], input_tensors[self._right_idx]
+        if left.stride(1) != 1 and p.K != 1:
+            left = left.contiguous()
+        device = left.device
+        desc.a = left.data_ptr()
+        desc.b = right.data_ptr()
+        operands = desc.operands
+        for slot, idx in enumerate(self._slot_inputs):
+            operands[slot].ptr = input_tensors[idx].data_ptr()
+        outputs: list[torch.Tensor] = []
+        primary = None
+        if spec.store_output:
+            primary = torch.empty_strided((p.M, p.N), (p.N, 1), dtype=self._output_descriptor.dtype, device=device)
+            desc.d = primary.data_ptr()
+        aux_out = []
+        for aux_index, slot in self._aux_slots.items():
+            d = self._intermediate_descriptors[aux_index]
+            t = torch.empty_strided((p.M, p.N), (p.N, 1), dtype=d.dtype, device=device)
+            operands[slot].ptr = t.data_ptr()
+            aux_out.append(t)
+        red_out = []
+        if self._reductions:
+            shape = (p.red_len,) if self._reductions[0].axis != 2 else ()
+            for r in self._reductions:
+                t = torch.empty(shape, dtype=torch.float32, device=device)
+                setattr(desc.reduce, _RED_FIELD[r.op], t.data_ptr())
+                red_out.append(t)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        if p.ws_bytes:
+            ws = p.ws.get(stream)
+            if ws is None:
+                ws = p.ws[stream] = torch.empty(p.ws_bytes, dtype=torch.uint8, device=device)
+            desc.reduce.workspace = ws.data_ptr()
+            desc.reduce.workspace_bytes = p.ws_bytes
+        if device.index is not None and device.index != torch.cuda.current_device():
+            with torch.cuda.device(device):
+                rc = self._lib.fuseml_sm100_gemm_epilogue(C.byref(desc), C.byref(p.plan), C.c_void_p(stream))
+        else:
+            rc = self._lib.fuseml_sm100_gemm_epilogue(C.byref(desc), C.byref(p.plan), C.c_void_p(stream))
+        if rc != N.OK:
+            N.check(rc, "fuseml_sm100_gemm_epilogue")
+        self.launch_count += 1
+        # reductions come back in fp32; hand them over in the dtype the graph expects
+        red_out = [t if t.dtype == dt else t.to(dt) for t, dt in zip(red_out, self._reduction_dtypes)]
+        if primary is not None:
+            outputs.append(primary)
+        outputs.extend(aux_out)
+        if primary is None and red_out and not aux_out and len(red_out) == 1:
+            return red_out[0]
+        if primary is None and red_out:   # the first reduction is the group's primary output
+            return (red_out[0], *aux_out, *red_out[1:])
+        outputs.extend(red_out)
+        return outputs[0] if len(outputs) == 1 else tuple(outputs)
+
+    def __repr__(self) -> str:
+        ins = [d.name for d in self._input_descriptors]
+        red = f", reductions={[(r.op, r.axis) for r in self._reductions]}" if self._reductions else ""
+        lp = self._launch_params
+        blk = f"block=({lp.block_m},{lp.block_n},{lp.block_k})" if lp is not None else "block=(router)"
+        return (f"KernelLauncher(inputs={ins}, output={self._output_descriptor.name!r}, "
+                f"intermediates={[d.name for d in self._intermediate_descriptors]}, {blk}{red})")

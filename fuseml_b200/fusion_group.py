@@ -30,6 +30,9 @@ class FusionGroup:
     # extensions (see FuseMLFusionPass options)
     extra_outputs: list = field(default_factory=list)   # further reduction nodes fed by the same tensor
     store_output: bool = True                           # False: only reductions leave the kernel
+    # inputs as discovery saw them; surgery later swaps entries of ``inputs`` for the fused
+    # nodes that replaced them, while recorded node args still name the originals
+    original_inputs: list = field(default_factory=list)
 
     def __post_init__(self) -> None:
         if self.output_node is None:
