@@ -71,41 +71,83 @@ class TransformerMLP(nn.Module):
         return self.linear2(F.gelu(self.linear1(x))) + x
 
 
+class StackedMLP(nn.Module):
+    """``blocks`` residual MLP blocks; with ``reductions`` also the global sum and amax of the output."""
+
+    def __init__(self, d_model, d_intermediate, blocks, reductions):
+        super().__init__()
+        self.blocks = nn.ModuleList([TransformerMLP(d_model, d_intermediate) for _ in range(blocks)])
+        self.reductions = reductions
+
+    def forward(self, x):
+        for blk in self.blocks:
+            x = blk(x)
+        if self.reductions:
+            return x, x.sum(), x.amax()
+        return x
+
+
+class ActHeavy(nn.Module):
+    def __init__(self, W, b):
+        super().__init__()
+        self.W = nn.Parameter(W, requires_grad=False)
+        self.b = nn.Parameter(b, requires_grad=False)
+
+    def forward(self, x, r):
+        h = torch.addmm(self.b, x, self.W)
+        return F.gelu(h) * torch.sigmoid(h) + r
+
+
+class GemmReduce(nn.Module):
+    def __init__(self, B):
+        super().__init__()
+        self.B = nn.Parameter(B, requires_grad=False)
+
+    def forward(self, a):
+        c = torch.relu(a @ self.B)
+        return c.amax(-1), c.mean(-1)
+
+
 class Workload:
-    """Resident tensors + one ``step()`` (a pass of the hot path over one batch)."""
+    """Resident tensors + ``step()`` (one pass of the hot path over one batch) + ``e2e_step()``
+    (the same pass fed from pinned host memory, result read back).  Every pass goes through the
+    public entry point, ``torch.compile(module, backend=FuseMLCompiler())``."""
 
     name = ""
     dtype = "bf16"
     bound = "tensor"
+    expected_kernels = 1
 
-    def step(self):
-        raise NotImplementedError
+    def _compile(self, module):
+        import fuseml_b200 as FM
 
-    def e2e_step(self):
-        raise NotImplementedError
+        self.compiler = FM.FuseMLCompiler()
+        self.module = module.eval()
+        self.compiled = torch.compile(self.module, backend=self.compiler)
+
+    def check_compiled(self):
+        c = self.compiler
+        if not c.fusion_applied or len(c.launchers) != self.expected_kernels:
+            raise SystemExit(f"{self.name}: expected {self.expected_kernels} fused kernels, compiler built "
+                             f"{len(c.launchers)} (declined: {c.declined})")
+
+    def fused_launches(self):
+        return sum(L.launch_count for L in set(self.compiler.launchers))
 
 
 class MLPBlock(Workload):
     """cfg4 (blocks=1) and cfg5 (blocks=4 + global sum/amax [+ allreduce])."""
 
     def __init__(self, rows, d_model=4096, d_inter=16384, blocks=1, reductions=False, world=1, seed=0):
-        from fuseml_b200 import kernels as K
-
-        self.K = K
         self.rows, self.D, self.I, self.blocks, self.reductions, self.world = rows, d_model, d_inter, blocks, reductions, world
         self.name = "cfg5_stacked_mlp_x4" if blocks > 1 else "cfg4_mlp_block"
         torch.manual_seed(seed)
-        mods = [TransformerMLP(d_model, d_inter) for _ in range(blocks)]
-        self.params = []
-        for m in mods:
-            self.params.append(tuple(t.detach().to(torch.bfloat16).cuda() for t in
-                                     (m.linear1.weight, m.linear1.bias, m.linear2.weight, m.linear2.bias)))
+        self._compile(StackedMLP(d_model, d_inter, blocks, reductions).to(device="cuda", dtype=torch.bfloat16))
+        self.expected_kernels = 2 * blocks
         g = torch.Generator().manual_seed(seed + 1 + int(os.environ.get("RANK", "0")))
         self.x_host = torch.randn(rows, d_model, generator=g).to(torch.bfloat16).pin_memory()
         self.y_host = torch.empty(rows, d_model, dtype=torch.bfloat16).pin_memory()
         self.x = self.x_host.cuda()
-        self.h = torch.empty(rows, d_inter, dtype=torch.bfloat16, device="cuda")
-        self.bufs = [torch.empty(rows, d_model, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
         self.x_in = torch.empty_like(self.x)
         self.tokens = rows
         self.flops_per_launch = 2.0 * rows * d_model * d_inter
@@ -119,26 +161,19 @@ class MLPBlock(Workload):
         self.scalars = None
 
     def _forward(self, x):
-        K = self.K
-        cur = x
-        reds = None
-        for i, (w1, b1, w2, b2) in enumerate(self.params):
-            K.fused_gemm(cur, w1.t(), K.EpilogueProgram().bias(b1).gelu(), out=self.h)
-            out = self.bufs[i % 2]
-            last = self.reductions and i == self.blocks - 1
-            prog = K.EpilogueProgram().bias(b2).add_tensor(cur)
-            if last:
-                _, reds = K.fused_gemm(self.h, w2.t(), prog, out=out, reduce=("sum", "max"), axis=None)
-            else:
-                K.fused_gemm(self.h, w2.t(), prog, out=out)
-            cur = out
-        if reds is not None and self.world > 1:
+        with torch.no_grad():
+            out = self.compiled(x)
+        if not self.reductions:
+            return out
+        y, s, m = out
+        if self.world > 1:
             import torch.distributed as dist
 
-            dist.all_reduce(reds["sum"], op=dist.ReduceOp.SUM)
-            dist.all_reduce(reds["max"], op=dist.ReduceOp.MAX)
-        self.scalars = reds
-        return cur
+            s, m = s.float(), m.float()
+            dist.all_reduce(s, op=dist.ReduceOp.SUM)
+            dist.all_reduce(m, op=dist.ReduceOp.MAX)
+        self.scalars = (s, m)
+        return y
 
     def step(self):
         return self._forward(self.x)
@@ -148,7 +183,7 @@ class MLPBlock(Workload):
         y = self._forward(self.x_in)
         self.y_host.copy_(y, non_blocking=True)
         if self.scalars is not None:
-            return float(self.scalars["sum"]) + float(self.scalars["max"])  # device->host read of the metrics
+            return float(self.scalars[0]) + float(self.scalars[1])  # device->host read of the metrics
         torch.cuda.current_stream().synchronize()
         return None
 
@@ -160,21 +195,18 @@ class ActHeavyGemm(Workload):
     bound = "hbm"
 
     def __init__(self, rows=256, Kd=4096, Nn=16384, seed=0, copies=3):
-        from fuseml_b200 import kernels as K
-
-        self.K = K
         torch.manual_seed(seed)
         lin = nn.Linear(Kd, Nn)
         W = lin.weight.detach().t().contiguous().to(torch.bfloat16).cuda()
+        b = lin.bias.detach().to(torch.bfloat16).cuda()
+        self._compile(ActHeavy(W, b))
         # rotate several copies of the 128 MB weight so that no launch finds it in the 126 MB L2
         self.Ws = [W] + [W.clone() for _ in range(copies - 1)]
-        self.b = lin.bias.detach().to(torch.bfloat16).cuda()
         self.x_host = torch.randn(rows, Kd).to(torch.bfloat16).pin_memory()
         self.r_host = torch.randn(rows, Nn).to(torch.bfloat16).pin_memory()
         self.y_host = torch.empty(rows, Nn, dtype=torch.bfloat16).pin_memory()
         self.x, self.r = self.x_host.cuda(), self.r_host.cuda()
         self.x_in, self.r_in = torch.empty_like(self.x), torch.empty_like(self.r)
-        self.out = torch.empty(rows, Nn, dtype=torch.bfloat16, device="cuda")
         self.i = 0
         self.tokens = rows
         self.flops_per_launch = self.flops = 2.0 * rows * Kd * Nn
@@ -184,11 +216,10 @@ class ActHeavyGemm(Workload):
         self.d2h_bytes = rows * Nn * 2
 
     def _forward(self, x, r):
-        K = self.K
-        W = self.Ws[self.i % len(self.Ws)]
+        self.module.W.data = self.Ws[self.i % len(self.Ws)]   # same shape / stride: no recompilation
         self.i += 1
-        prog = K.EpilogueProgram().bias(self.b).save().gelu().swap().sigmoid().mul_saved().add_tensor(r)
-        return K.fused_gemm(x, W, prog, out=self.out)
+        with torch.no_grad():
+            return self.compiled(x, r)
 
     def step(self):
         return self._forward(self.x, self.r)
@@ -207,36 +238,32 @@ class GemmRowReduce(Workload):
     name = "cfg3_gemm_row_reductions"
 
     def __init__(self, rows=8192, Kd=4096, Nn=4096, seed=0):
-        from fuseml_b200 import kernels as K
-
-        self.K = K
         torch.manual_seed(seed)
         self.a_host = torch.randn(rows, Kd).to(torch.bfloat16).pin_memory()
         self.A = self.a_host.cuda()
         self.A_in = torch.empty_like(self.A)
-        self.B = (torch.randn(Kd, Nn) / Kd ** 0.5).to(torch.bfloat16).cuda()
-        self.out_host = torch.empty(2, rows, dtype=torch.float32).pin_memory()
+        self._compile(GemmReduce((torch.randn(Kd, Nn) / Kd ** 0.5).to(torch.bfloat16).cuda()))
+        self.out_host = torch.empty(2, rows, dtype=torch.bfloat16).pin_memory()
         self.tokens = rows
         self.flops_per_launch = self.flops = 2.0 * rows * Kd * Nn
         self.algo_bytes = 2.0 * (rows * Kd + Kd * Nn) + 8.0 * rows
         self.launches_per_step = 2
         self.gemm_launches_per_step = 1
         self.h2d_bytes = rows * Kd * 2
-        self.d2h_bytes = rows * 8
+        self.d2h_bytes = rows * 4
 
     def _forward(self, A):
-        K = self.K
-        _, reds = K.fused_gemm(A, self.B, K.EpilogueProgram().relu(), store=False, reduce=("max", "mean"), axis=-1)
-        return reds
+        with torch.no_grad():
+            return self.compiled(A)
 
     def step(self):
         return self._forward(self.A)
 
     def e2e_step(self):
         self.A_in.copy_(self.a_host, non_blocking=True)
-        reds = self._forward(self.A_in)
-        self.out_host[0].copy_(reds["max"], non_blocking=True)
-        self.out_host[1].copy_(reds["mean"], non_blocking=True)
+        mx, mean = self._forward(self.A_in)
+        self.out_host[0].copy_(mx, non_blocking=True)
+        self.out_host[1].copy_(mean, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
 
@@ -432,10 +459,13 @@ def main():
 
     for _ in range(W):
         wl.step()
+    wl.check_compiled()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    launches_before = wl.fused_launches()
     total_ms = timed(wl.step, steps)
+    launches_timed = wl.fused_launches() - launches_before
     clocks = sampler.stop() if rank == 0 else {}
     status = K.device_status()
     if status != 0:
@@ -478,7 +508,7 @@ def main():
                    "parallelism": f"rows sharded over {world} GPU(s), weights replicated"},
         "e2e": {"value": wl.tokens * world / (e2e_ms / steps * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes, "ms_per_step": e2e_ms / steps},
-        "gpu_launches": wl.launches_per_step * steps,
+        "gpu_launches": launches_timed + (steps if wl.launches_per_step > wl.gemm_launches_per_step else 0),
         "roofline": roof,
         "clocks": clocks,
         "tflops": wl.flops * world / (ms_per_step * 1e-3) / 1e12,

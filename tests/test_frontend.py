@@ -1,0 +1,198 @@
+"""Front end on CPU: discovery against the reference's own groups (tests/golden/structure.json),
+the opt-in extensions, lowering to kernel specifications, cache / launcher host logic, and —
+when the reference checkout is present — the reference's own pass-level tests run against
+this package through the ``fuseml`` alias."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+from torch.fx.experimental.proxy_tensor import make_fx
+from torch.fx.passes.shape_prop import ShapeProp
+
+import fuseml_b200 as F
+from fuseml_b200 import _native as N
+from fuseml_b200.codegen.kernel_generator import Sm100KernelGenerator, UnsupportedChainError
+from oracle import configs
+
+ROOT = Path(__file__).resolve().parent.parent
+REFERENCE = Path("/root/reference")
+CFGS = list(configs.MAKERS)
+
+
+def _trace(case):
+    with torch.no_grad():
+        gm = make_fx(lambda *a: case.module(*a))(*case.args)
+    ShapeProp(gm).propagate(*case.args)
+    return gm
+
+
+def _specs(gm):
+    gen = Sm100KernelGenerator()
+    out = []
+    for n in gm.graph.nodes:
+        g = n.meta.get("fusion_group")
+        if g is not None:
+            out.append((g, gen.build_spec(g)))
+    return out
+
+
+@pytest.mark.parametrize("name", CFGS)
+def test_default_discovery_equals_reference(golden_dir, name):
+    golden = json.loads((golden_dir / "structure.json").read_text())[name]
+    case = configs.make(name, small=(name != "cfg1"))
+    groups = F.FuseMLFusionPass(_trace(case))._find_fusion_groups()
+    assert [list(g.op_signature) for g in groups] == [g["op_signature"] for g in golden]
+    assert [len(g.inputs) for g in groups] == [g["n_inputs"] for g in golden]
+    assert [list(g.output_metadata.get("shape", ())) for g in groups] == [g["output_shape"] for g in golden]
+    assert [len(g.intermediate_outputs) for g in groups] == [g["intermediate_outputs"] for g in golden]
+    for g, ref in zip(groups, golden):
+        assert [n.op for n in g.inputs] == ref["input_kinds"]
+
+
+def test_extensions_fuse_what_the_reference_cannot():
+    opts = dict(dag_epilogue=True, multi_reduction=True, global_reductions=True)
+    # cfg2: addmm has two users -> one diamond group, evaluated with the second register
+    gm = _trace(configs.make("cfg2", small=True))
+    F.FuseMLFusionPass(gm, **opts).run()
+    (g, spec), = _specs(gm)
+    assert list(g.op_signature) == ["aten.addmm.default", "aten.gelu.default", "aten.sigmoid.default",
+                                    "aten.mul.Tensor", "aten.add.Tensor"]
+    assert [N.OP_NAMES[s.opcode] for s in spec.steps] == ["add_t", "save", "gelu_erf", "swap", "sigmoid",
+                                                          "mul_saved", "add_t"]
+    assert spec.uses_second_register and spec.store_output and not spec.reductions
+    # cfg3: both reductions in one kernel, the matrix is never stored
+    gm = _trace(configs.make("cfg3", small=True))
+    F.FuseMLFusionPass(gm, **opts).run()
+    (g, spec), = _specs(gm)
+    assert [(r.op, r.axis) for r in spec.reductions] == [("max", 1), ("mean", 1)]
+    assert not spec.store_output and len(g.extra_outputs) == 1
+    # cfg5: last block stores its output and also yields the global sum and amax
+    gm = _trace(configs.make("cfg5", small=True))
+    F.FuseMLFusionPass(gm, **opts).run()
+    specs = _specs(gm)
+    assert len(specs) == 8
+    last = specs[-1][1]
+    assert last.store_output and [(r.op, r.axis) for r in last.reductions] == [("sum", 2), ("max", 2)]
+    # the graph now returns getitem(fused, 0..2)
+    out = next(n for n in gm.graph.nodes if n.op == "output")
+    assert all(a.target.__name__ == "getitem" for a in out.args[0])
+
+
+def test_lowering_of_addmm_scaling_and_scalars():
+    def f(bias, x, w, r):
+        h = torch.addmm(bias, x, w, beta=0.5, alpha=2.0)
+        h = torch.relu(h) * 3.0
+        h = h + 1.5
+        return torch.add(h, r, alpha=2.0)
+    args = (torch.randn(8), torch.randn(4, 16), torch.randn(16, 8), torch.randn(4, 8))
+    gm = make_fx(f)(*args)
+    ShapeProp(gm).propagate(*args)
+    F.FuseMLFusionPass(gm).run()
+    (_, spec), = _specs(gm)
+    names = [(N.OP_NAMES[s.opcode], round(s.imm, 6)) for s in spec.steps]
+    assert names == [("mul_imm", 4.0), ("add_t", 0.0), ("mul_imm", 0.5), ("relu", 0.0), ("mul_imm", 3.0),
+                     ("add_imm", 1.5), ("mul_imm", 0.5), ("add_t", 0.0), ("mul_imm", 2.0)]
+    assert (spec.left_index, spec.right_index) == (1, 2)
+
+
+def test_lowering_rejects_what_the_vm_cannot_express():
+    def f(a, b):
+        return torch.mm(a, b).amax(-1, keepdim=True)
+    args = (torch.randn(4, 8), torch.randn(8, 4))
+    gm = make_fx(f)(*args)
+    ShapeProp(gm).propagate(*args)
+    assert F.FuseMLFusionPass(gm)._find_fusion_groups() == []      # keepdim=True is never absorbed
+    # gelu(approximate='tanh') lowers to its own opcode instead of silently using erf
+    def g(a, b):
+        return torch.nn.functional.gelu(torch.mm(a, b), approximate="tanh")
+    gm = make_fx(g)(*args)
+    ShapeProp(gm).propagate(*args)
+    F.FuseMLFusionPass(gm).run()
+    (_, spec), = _specs(gm)
+    assert [N.OP_NAMES[s.opcode] for s in spec.steps] == ["gelu_tanh"]
+
+
+def test_compiler_on_cpu_hands_back_eager_like_the_reference(golden_dir):
+    """On CPU tensors nothing is lowered (no CPU implementation of the fused path exists)."""
+    import numpy as np
+
+    case = configs.make("cfg1")
+    comp = F.FuseMLCompiler()
+    out = torch.compile(case.module, backend=comp)(*case.args)
+    assert comp.fusion_applied is False and comp.fusion_strategy == "none" and comp.launchers == []
+    np.testing.assert_allclose(out.detach().numpy(), np.load(golden_dir / "numeric_cfg1.npz")["y"], rtol=1e-5, atol=1e-5)
+    torch._dynamo.reset()
+
+
+def test_launcher_host_contract():
+    from fuseml_b200.codegen.kernel_generator import KernelSpec, TensorDescriptor
+
+    spec = KernelSpec(left_index=1, right_index=2, n_inputs=3)
+    d = [TensorDescriptor("bias", (8,), (1,), torch.bfloat16), TensorDescriptor("x", (4, 16), (16, 1), torch.bfloat16),
+         TensorDescriptor("w", (16, 8), (1, 16), torch.bfloat16)]
+    out = TensorDescriptor("out", (4, 8), (8, 1), torch.bfloat16)
+    L = F.KernelLauncher(spec, d, out, [], "x", "w")
+    assert L.__name__ == "fuseml_fused_kernel"
+    with pytest.raises(ValueError, match="Expected 3 input"):
+        L(torch.zeros(1))
+    with pytest.raises(ValueError, match="left_name"):
+        F.KernelLauncher(spec, d, out, [], "nope", "w")
+    with pytest.raises(ValueError, match="disagree"):
+        F.KernelLauncher(spec, d, out, [], "w", "x")
+    with pytest.raises(RuntimeError):      # CPU tensors: no fallback, a loud error
+        L(torch.zeros(8, dtype=torch.bfloat16), torch.zeros(4, 16, dtype=torch.bfloat16),
+          torch.zeros(8, 16, dtype=torch.bfloat16).t())
+
+
+def test_launch_params_and_tile_chooser():
+    lp = F.compute_launch_params(8192, 16384, 4096, torch.bfloat16)
+    assert (lp.block_m, lp.block_n, lp.block_k, lp.num_stages) == (128, 256, 64, 4)
+    assert F.compute_sram_bytes(128, 256, 64, 2, 4) == 4 * (16384 + 32768)
+    tuner = F.SRAMAutotuner()
+    cfg = tuner.get_best_config(8192, 16384, 4096, torch.bfloat16)
+    assert cfg.block_m == 128 and cfg.block_n == 256 and cfg.sram_bytes <= tuner.sram_budget and cfg.tmem_cols == 512
+    assert tuner.get_best_config(8192, 16384, 4096, torch.bfloat16) is cfg and tuner.cache_size == 1
+    small = F.SRAMAutotuner(sram_budget=100 * 1024)
+    assert small.get_best_config(8192, 16384, 4096).sram_bytes <= 100 * 1024
+    assert all(c.sram_bytes <= 64 * 1024 for c in F.generate_sram_safe_configs(torch.bfloat16, 64 * 1024))
+
+
+def test_library_epilogue_patterns_are_programs_now():
+    gm = _trace(configs.make("cfg4", small=True))
+    triggers = [n for n in gm.graph.nodes if F.is_trigger(n)]
+    pats = [F.match_cublas_epilogue(t) for t in triggers]
+    assert [p.epilogue_type for p in pats] == ["GELU_BIAS", "BIAS_RESIDUAL"]
+    assert pats[0].program() == ("add_t", "gelu_erf") and pats[1].program() == ("add_t", "add_t")
+    assert F.cublas_epilogue_available() is False
+
+
+def test_fuseml_alias_package():
+    import fuseml
+    from fuseml.passes.fusion_pass import FuseMLFusionPass as P1
+    from fuseml.codegen.kernel_cache import KernelCache as C1
+
+    assert P1 is F.FuseMLFusionPass and C1 is F.KernelCache and fuseml.FuseMLCompiler is F.FuseMLCompiler
+
+
+REF_TESTS = ["test_registry", "test_fusion_group", "test_pattern_matching", "test_graph_surgery",
+             "test_get_attr_resolution", "test_shape_propagation", "test_aot_topology", "test_graph_cut",
+             "test_mutation_safety", "test_control_flow_validation", "test_end_to_end", "test_kernel_cache"]
+
+
+@pytest.mark.skipif(not (REFERENCE / "tests").is_dir(), reason="reference checkout not present on this machine")
+def test_reference_pass_level_suite_passes_against_this_package(tmp_path):
+    """Run the reference's own structural tests, unmodified and in place, with ``fuseml``
+    resolving to this package."""
+    env = dict(os.environ, PYTHONPATH=str(ROOT), PYTHONDONTWRITEBYTECODE="1")
+    files = [str(REFERENCE / "tests" / f"{t}.py") for t in REF_TESTS]
+    proc = subprocess.run([sys.executable, "-m", "pytest", "-q", "-p", "no:cacheprovider", f"--rootdir={tmp_path}", *files],
+                          cwd=tmp_path, env=env, capture_output=True, text=True, timeout=600)
+    tail = proc.stdout.strip().splitlines()[-1] if proc.stdout.strip() else proc.stderr[-500:]
+    assert proc.returncode == 0, proc.stdout[-3000:]
+    assert "passed" in tail and "failed" not in tail
