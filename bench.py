@@ -341,9 +341,21 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                 "-lms", "50"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+
+    def samples_so_far(self):
+        try:
+            return sum(1 for l in open(self.path) if l.strip())
+        except Exception:
+            return 0
+
+    def wait_for_samples(self, n, timeout_s=3.0):
+        """nvidia-smi takes a moment to start: block (bounded) until it has written n samples."""
+        t0 = time.perf_counter()
+        while self.proc is not None and self.samples_so_far() < n and time.perf_counter() - t0 < timeout_s:
+            time.sleep(0.02)
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
@@ -359,24 +371,24 @@ class ClockSampler:
             os.unlink(self.path)
         except Exception:
             return out
-        sm, reasons, mx, pw = [], set(), None, []
+        samples, mx = [], None
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in rows:
             if len(r) < 7:
                 continue
             try:
-                sm.append(float(r[0])); mx = float(r[1]); pw.append(float(r[2]))
+                clk, mx, watts = float(r[0]), float(r[1]), float(r[2])
             except ValueError:
                 continue
-            for nm, v in zip(names, r[3:7]):
-                if v.strip().lower() == "active":
-                    reasons.add(nm)
-        if sm:
-            # median of the upper half: samples taken while the GPU was under load
-            sm.sort()
-            upper = sm[len(sm) // 2:]
-            out.update(sm_mhz=upper[len(upper) // 2], sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm),
-                       power_w_max=max(pw) if pw else None)
+            samples.append((clk, watts, {nm for nm, v in zip(names, r[3:7]) if v.strip().lower() == "active"}))
+        if samples:
+            # "under load" = samples drawing at least half of the highest power seen in the window
+            p_max = max(w for _, w, _ in samples)
+            loaded = [x for x in samples if x[1] >= 0.5 * p_max] or samples
+            clks = sorted(c for c, _, _ in loaded)
+            reasons = set().union(*[rs for _, _, rs in loaded])
+            out.update(sm_mhz=clks[len(clks) // 2], sm_max_mhz=mx, reasons=sorted(reasons), samples=len(samples),
+                       samples_under_load=len(loaded), power_w_max=p_max)
         return out
 
 
@@ -435,6 +447,9 @@ def main():
     _native.load()
     W = max(3, args.warmup)
     steps = max(1, args.steps)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     wl = make_workload(args.workload, world, args.scaling)
 
     def barrier():
@@ -460,13 +475,21 @@ def main():
     for _ in range(W):
         wl.step()
     wl.check_compiled()
-    sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()
+        sampler.wait_for_samples(1)     # started before the workload was built; normally no wait
     launches_before = wl.fused_launches()
     total_ms = timed(wl.step, steps)
     launches_timed = wl.fused_launches() - launches_before
+    # The timed region may be shorter than one sampling period (50 ms): repeat the same step,
+    # untimed, so that the window under load is at least 0.4 s.  The count is derived from the
+    # all-reduced time, so every rank runs the same number of steps (and collectives).
+    extra = max(0, int(400.0 / max(total_ms / steps, 1e-3)) - steps)
+    for _ in range(min(extra, 20000)):
+        wl.step()
+    torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else {}
+    if rank == 0:
+        clocks["window"] = "timed region plus untimed repeats of the same step (>= 0.4 s under load)"
     status = K.device_status()
     if status != 0:
         raise SystemExit(f"device status {status:#x}: a bounded wait ran out; numbers would be meaningless")

@@ -63,6 +63,14 @@ __global__ void reduce_finalize_kernel(const float* __restrict__ psum, const flo
   }
 }
 
+// Neutral elements for partial arrays (0 for sums, -inf for maxima).
+__global__ void fill_neutral_kernel(float* __restrict__ psum, float* __restrict__ pmax, int n) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    if (psum) psum[i] = 0.0f;
+    if (pmax) pmax[i] = -INFINITY;
+  }
+}
+
 __device__ __forceinline__ float tail_load(const void* x, int64_t idx, int32_t dtype) {
   if (dtype == FUSEML_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[idx]);
   if (dtype == FUSEML_F16) return __half2float(reinterpret_cast<const __half*>(x)[idx]);

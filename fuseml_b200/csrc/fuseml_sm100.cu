@@ -11,7 +11,7 @@
 
 #include "../../include/fuseml_sm100.h"
 #include "aux_kernels.cuh"
-#include "gemm_kernel.cuh"
+#include "gemm_kernel_v2.cuh"
 #include "host_plan.h"
 
 namespace fuseml {
@@ -60,34 +60,64 @@ static int encode_2d(CUtensorMap* tm, int32_t dtype, const void* base, int64_t r
   return r == CUDA_SUCCESS ? FUSEML_OK : FUSEML_E_LAYOUT;
 }
 
-template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED>
+template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED, int CG>
 static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
                            cudaStream_t stream) {
-  using L = SmemLayout<BN, STAGES>;
-  auto kernel = gemm_epilogue_kernel<BN, STAGES, FMT, B_MN, SAVED>;
-  static bool configured = false;  // per instantiation; the attribute is sticky per device function
-  static int configured_device = -1;
+  using L = v2::Smem<BN, STAGES, CG>;
+  auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, FMT, B_MN, SAVED, CG>;
+  static int configured_device = -1;   // per instantiation; the attribute is sticky per device function
+  static int max_clusters = 0;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!configured || configured_device != dev) {
+  if (configured_device != dev) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes) != cudaSuccess) {
       cudaGetLastError();
       return FUSEML_E_LAUNCH;
     }
-    configured = true;
+    max_clusters = 0;
+    if (CG == 2) {
+      // how many CTA pairs the device can hold at once (GPCs with an odd SM count lose one SM)
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2 * 148);
+      q.blockDim = dim3(v2::kThreads);
+      q.dynamicSmemBytes = L::kDynamicBytes;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 0; }
+      max_clusters = n;
+    }
     configured_device = dev;
   }
-  kernel<<<grid, kNumThreads, L::kDynamicBytes, stream>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  if (CG == 2) {
+    int pairs = grid / 2;
+    if (max_clusters > 0 && pairs > max_clusters) pairs = max_clusters;
+    if (pairs < 1) pairs = 1;
+    grid = 2 * pairs;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+  }
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(v2::kThreads);
+  cfg.dynamicSmemBytes = L::kDynamicBytes;
+  cfg.stream = stream;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+  if (e != cudaSuccess) { cudaGetLastError(); return FUSEML_E_LAUNCH; }
+  return FUSEML_OK;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CG>
 static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int fmt, bool b_mn,
                      int grid, cudaStream_t stream) {
   const bool saved = p.uses_saved != 0;
 #define FUSEML_DISPATCH(F, MN)                                                              \
-  return saved ? launch_instance<BN, STAGES, F, MN, true>(ta, tb, p, grid, stream)          \
-               : launch_instance<BN, STAGES, F, MN, false>(ta, tb, p, grid, stream)
+  return saved ? launch_instance<BN, STAGES, F, MN, true, CG>(ta, tb, p, grid, stream)      \
+               : launch_instance<BN, STAGES, F, MN, false, CG>(ta, tb, p, grid, stream)
   if (fmt == 2) { FUSEML_DISPATCH(2, false); }
   if (fmt == 1) { if (b_mn) { FUSEML_DISPATCH(1, true); } else { FUSEML_DISPATCH(1, false); } }
   if (b_mn) { FUSEML_DISPATCH(0, true); } else { FUSEML_DISPATCH(0, false); }
@@ -98,7 +128,8 @@ static int check_plan(const fuseml_plan_t* pl) {
   if (pl->tile_m != 128) return FUSEML_E_PLAN;
   if (pl->tile_n != 128 && pl->tile_n != 256) return FUSEML_E_PLAN;
   if (pl->grid <= 0 || pl->group_m <= 0) return FUSEML_E_PLAN;
-  if (pl->cluster != 1) return FUSEML_E_PLAN;
+  if (pl->cluster != 1 && pl->cluster != 2) return FUSEML_E_PLAN;
+  if (pl->cluster == 2 && pl->tile_n != 256) return FUSEML_E_PLAN;
   return FUSEML_OK;
 }
 
@@ -230,7 +261,9 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   CUtensorMap ta, tb;
   rc = encode_2d(&ta, desc->ab_dtype, a_ptr, desc->M, K, lda, BK, kTileM);
   if (rc != FUSEML_OK) return rc;
-  if (!b_mn) rc = encode_2d(&tb, desc->ab_dtype, b_ptr, desc->N, K, ldb, BK, BN);
+  // K-major B: one box per CTA covers that CTA's share of the tile's columns (all of them for a
+  // single CTA, half for a CTA pair)
+  if (!b_mn) rc = encode_2d(&tb, desc->ab_dtype, b_ptr, desc->N, K, ldb, BK, BN / plan.cluster);
   else rc = encode_2d(&tb, desc->ab_dtype, b_ptr, K, desc->N, ldb, 64, BK);
   if (rc != FUSEML_OK) return rc;
 
@@ -239,7 +272,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   p.M = static_cast<int32_t>(desc->M);
   p.N = static_cast<int32_t>(desc->N);
   p.K = static_cast<int32_t>(K);
-  p.tiles_m = static_cast<int32_t>((desc->M + kTileM - 1) / kTileM);
+  const int CGr = plan.cluster;
+  p.tiles_m = static_cast<int32_t>((desc->M + kTileM * CGr - 1) / (kTileM * CGr));
   p.tiles_n = static_cast<int32_t>((desc->N + BN - 1) / BN);
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.group_m = std::min(plan.group_m, p.tiles_m);
@@ -270,15 +304,19 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   if (cudaGetSymbolAddress(&status_ptr, g_status_word) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
   p.status = reinterpret_cast<int32_t*>(status_ptr);
 
-  int grid = std::min(plan.grid, p.num_tiles);
-  if (desc->reduce.kinds != 0 && desc->reduce.axis == FUSEML_AXIS_ALL) grid = std::min<int>(grid, static_cast<int>(w.partials));
-  if (BN == 256) rc = launch_bn<256, 4>(ta, tb, p, fmt, b_mn, grid, stream);
-  else rc = launch_bn<128, 6>(ta, tb, p, fmt, b_mn, grid, stream);
+  int grid = std::min(plan.grid, p.num_tiles * CGr);
+  if (desc->reduce.kinds != 0 && desc->reduce.axis == FUSEML_AXIS_ALL) {
+    // AXIS_ALL partials: one per launched CTA.  Slots of CTAs that end up not launched (the
+    // device holds fewer CTA pairs than asked for) are filled with neutral values first.
+    grid = std::min<int>(grid, static_cast<int>(w.partials));
+    fill_neutral_kernel<<<1, 256, 0, stream>>>(p.red_sum, p.red_max, static_cast<int>(w.partials));
+  }
+  if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, p, fmt, b_mn, grid, stream);
+  else if (BN == 256) rc = launch_bn<256, 4, 1>(ta, tb, p, fmt, b_mn, grid, stream);
+  else rc = launch_bn<128, 6, 1>(ta, tb, p, fmt, b_mn, grid, stream);
   if (rc != FUSEML_OK) return rc;
 
   if (desc->reduce.kinds != 0) {
-    // AXIS_ALL partials: one per launched CTA
-    if (desc->reduce.axis == FUSEML_AXIS_ALL) w.partials = grid;
     const int64_t count = desc->reduce.axis == FUSEML_AXIS_N ? desc->N
                         : desc->reduce.axis == FUSEML_AXIS_M ? desc->M : desc->M * desc->N;
     rc = run_finalize(desc->reduce, w, ws, count, stream);

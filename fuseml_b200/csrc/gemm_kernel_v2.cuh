@@ -1,0 +1,425 @@
+// Persistent, warp-specialised GEMM + fused epilogue for sm_100a, one CTA or a CTA pair per tile.
+//
+//   warp 0      TMA producer: A and B tiles -> 128B-swizzled shared-memory ring
+//   warp 1      allocates TMEM; one thread (of the pair's leader CTA) issues tcgen05.mma with
+//               the fp32 accumulator in TMEM and frees ring stages with tcgen05.commit
+//   warps 2..9  epilogue: two warps per TMEM lane quarter, alternating 32-column chunks:
+//               tcgen05.ld, epilogue program in registers, 16-byte stores / reductions
+//
+// CG = 1: the CTA computes a 128 x BN tile.  CG = 2 (cluster of two CTAs, cta_group::2): the
+// pair computes 256 x BN; each CTA loads its own 128 rows of A and its own BN/2 columns of B,
+// the MMA reads B from both CTAs' shared memory, so every SM ingests a third less operand data
+// per flop.  No TMA multicast is used: each CTA fetches only what it alone needs.
+// Two accumulator buffers live in TMEM, so the epilogue of tile i overlaps the MMAs of tile
+// i+1.  Replaces the Triton template of the reference (fuseml/codegen/kernel_generator.py:
+// 1178-1593) and its cuBLAS Lt call sites (fuseml/codegen/cublas_epilogue.py:602-676).
+#pragma once
+
+#include "epilogue.cuh"
+#include "gemm_params.cuh"
+#include "ptx.cuh"
+
+namespace fuseml {
+namespace v2 {
+
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + kEpiWarps * 32;  // 320
+constexpr int kEpiSplit = 2;                   // warps sharing one TMEM lane quarter
+
+enum : int32_t {
+  kWhereProducerEmpty = 0x201,
+  kWhereMmaFull = 0x202,
+  kWhereMmaTmemEmpty = 0x203,
+  kWhereEpilogueTmemFull = 0x204,
+  kWhereProducerDrain = 0x205,
+};
+
+template <int BN, int STAGES, int CG>
+struct Smem {
+  static constexpr int kABytes = kTileM * kSwizzleBytes;          // this CTA's 128 rows of A
+  static constexpr int kBBytes = (BN / CG) * kSwizzleBytes;       // this CTA's share of B
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kRingBytes = STAGES * kStageBytes;
+  static constexpr int kColRedBytes = 4 * 2 * BN * 4;             // [quarter][sum|max][BN]
+  static constexpr int kBarOffset = kRingBytes + kColRedBytes;
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kTotalBytes = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamicBytes = kTotalBytes + 1024;
+};
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) x += __shfl_xor_sync(0xffffffffu, x, s);
+  return x;
+}
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, s));
+  return x;
+}
+
+// Transposing butterfly: lane r holds v[c] = value(row r, column c) on entry; lane c holds the
+// reduction over the 32 rows of column c in v[0] on exit (31 shuffles).
+template <bool kIsMax>
+__device__ __forceinline__ float warp_column_reduce(float (&v)[kChunkN], int lane) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int i = 0; i < s; ++i) {
+      const float send = upper ? v[i] : v[i + s];
+      const float keep = upper ? v[i + s] : v[i];
+      const float got = __shfl_xor_sync(0xffffffffu, send, s);
+      v[i] = kIsMax ? fmaxf(keep, got) : (keep + got);
+    }
+  }
+  return v[0];
+}
+
+// Ask L2 for the operand bytes one thread's row of the tile will read in the epilogue, long
+// before the accumulator is ready (the epilogue warps are idle during the K loop).
+__device__ __forceinline__ void prefetch_operands(const GemmParams& p, int64_t m, int32_t n_tile0, int32_t bn,
+                                                  bool row_ok, int lane) {
+  for (int op = 0; op < p.n_ops; ++op) {
+    const int32_t code = p.ops[op].opcode;
+    if (code != FUSEML_OP_ADD_T && code != FUSEML_OP_MUL_T && code != FUSEML_OP_SUB_T && code != FUSEML_OP_RSUB_T)
+      continue;
+    const EpiOperand& o = p.operands[p.ops[op].slot];
+    if (o.stride_n != 1) continue;
+    const int eb = o.dtype == FUSEML_F32 ? 4 : 2;
+    const int32_t cols = (n_tile0 + bn <= p.N) ? bn : (p.N - n_tile0);
+    if (cols <= 0) continue;
+    if (o.stride_m == 0) {
+      // one row shared by everybody: a few lanes cover it
+      const char* base = reinterpret_cast<const char*>(o.ptr) + static_cast<int64_t>(n_tile0) * eb;
+      if (lane * 128 < cols * eb) ptx::prefetch_l2(base + lane * 128);
+    } else if (row_ok) {
+      const char* base = reinterpret_cast<const char*>(o.ptr) + (m * o.stride_m + n_tile0) * eb;
+      for (int b = 0; b < cols * eb; b += 128) ptx::prefetch_l2(base + b);
+    }
+  }
+}
+
+// FMT: 0 = f16, 1 = bf16, 2 = tf32 (fp32 storage).  B_MN: B is row-major [K,N] in global
+// memory (MN-major tiles) instead of K-major.  CG: CTAs per tile (1 or 2).
+template <int BN, int STAGES, int FMT, bool B_MN, bool USES_SAVED, int CG>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ GemmParams p) {
+  using L = Smem<BN, STAGES, CG>;
+  constexpr int kElemBytes = (FMT == 2) ? 4 : 2;
+  constexpr int BK = kSwizzleBytes / kElemBytes;
+  constexpr int UMMA_K = 32 / kElemBytes;
+  constexpr int kKSteps = BK / UMMA_K;
+  constexpr int BN_CTA = BN / CG;                 // B columns this CTA loads
+  constexpr uint32_t kTmemCols = 2 * BN;
+  static_assert(!(B_MN && FMT == 2), "MN-major B is only wired for 16-bit operands");
+  static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair");
+  static_assert(!B_MN || (BN_CTA % 64 == 0), "MN-major B is loaded in 64-column boxes");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
+  volatile uint32_t* abort_flag = tmem_base_slot + 1;
+  float* colred = reinterpret_cast<float*>(smem + L::kRingBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;
+  const bool is_leader = (cta_rank == 0);
+  const int32_t unit = blockIdx.x / CG;            // tile walker id (CTA or pair)
+  const int32_t num_units = gridDim.x / CG;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);    // leader: one expect_tx arrival covering both CTAs' bytes
+      ptx::mbar_init(empty_bar(s), 1);   // one commit arrival (multicast to both CTAs when paired)
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tmem_full_bar(a), 1);
+      ptx::mbar_init(tmem_empty_bar(a), kEpiWarps * CG);   // leader collects both CTAs' epilogue warps
+    }
+    *abort_flag = 0u;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    if (CG == 2) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_base_slot)), kTmemCols);
+      ptx::tmem_relinquish();
+    }
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (CG == 2) {   // the peer's barriers must exist before anything signals them
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const int32_t num_kb = p.num_kb;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (every CTA) -----------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, issued = 0;
+      bool ok = true;
+      for (int32_t t = unit; t < p.num_tiles && ok; t += num_units) {
+        int32_t tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
+        const int32_t m0 = tm * (kTileM * CG) + static_cast<int32_t>(cta_rank) * kTileM;
+        const int32_t n0 = tn * BN + static_cast<int32_t>(cta_rank) * BN_CTA;
+        for (int32_t kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWhereProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_base + stage * L::kStageBytes;
+          const uint32_t b_dst = a_dst + L::kABytes;
+          if (CG == 1) {
+            ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
+            ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * BK, m0);
+            if (!B_MN) {
+              ptx::tma_load_2d(b_dst, &tmap_b, full_bar(stage), kb * BK, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / 64; ++j)
+                ptx::tma_load_2d(b_dst + j * (BK * kSwizzleBytes), &tmap_b, full_bar(stage), n0 + j * 64, kb * BK);
+            }
+          } else {
+            // bytes of both CTAs are counted on the leader's barrier
+            const uint32_t lead_full = ptx::mapa(full_bar(stage), 0);
+            if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
+            ptx::tma_load_2d_pair(a_dst, &tmap_a, lead_full, kb * BK, m0);
+            if (!B_MN) {
+              ptx::tma_load_2d_pair(b_dst, &tmap_b, lead_full, kb * BK, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / 64; ++j)
+                ptx::tma_load_2d_pair(b_dst + j * (BK * kSwizzleBytes), &tmap_b, lead_full, n0 + j * 64, kb * BK);
+            }
+          }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok && is_leader) {
+        // Giving up: let copies already in flight land before the CTA exits (a pair's bytes are all
+        // counted on the leader's barriers, and the partner cannot leave before the final cluster
+        // barrier, so the leader's wait covers both).
+        const uint32_t pending = issued < static_cast<uint32_t>(STAGES) ? issued : STAGES;
+        int s = stage;
+        uint32_t ph = phase;
+        for (uint32_t i = 0; i < pending; ++i) {
+          if (--s < 0) { s = STAGES - 1; ph ^= 1u; }
+          const uint64_t t0 = ptx::globaltimer_ns();
+          while (!ptx::mbar_try_wait(full_bar(s), ph)) {
+            if (ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
+              if (p.status) atomicCAS(p.status, 0, kWhereProducerDrain);
+              break;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ---------------------------
+    if (lane == 0 && is_leader) {
+      constexpr uint32_t idesc = ptx::make_idesc(FMT, 0u, B_MN ? 1u : 0u, kTileM * CG, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int32_t t = unit; t < p.num_tiles && ok; t += num_units) {
+        if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kWhereMmaTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int32_t kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.status, kWhereMmaFull)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + stage * L::kStageBytes;
+          const uint32_t b_addr = a_addr + L::kABytes;
+          const uint64_t a_desc = ptx::make_smem_desc_sw128(a_addr, 16u, 1024u);
+          const uint64_t b_desc = B_MN ? ptx::make_smem_desc_sw128(b_addr, BK * kSwizzleBytes, 1024u)
+                                       : ptx::make_smem_desc_sw128(b_addr, 16u, 1024u);
+          constexpr uint32_t kAStep = 32u >> 4;
+          constexpr uint32_t kBStep = B_MN ? ((UMMA_K * kSwizzleBytes) >> 4) : (32u >> 4);
+#pragma unroll
+          for (int k = 0; k < kKSteps; ++k) {
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            if (CG == 2) {
+              if (FMT == 2) ptx::mma_tf32_ss_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
+              else ptx::mma_f16_ss_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
+            } else {
+              if (FMT == 2) ptx::mma_tf32_ss(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
+              else ptx::mma_f16_ss(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
+            }
+          }
+          if (CG == 2) ptx::mma_commit_pair(empty_bar(stage)); else ptx::mma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (CG == 2) ptx::mma_commit_pair(tmem_full_bar(acc)); else ptx::mma_commit(tmem_full_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue (every CTA, 8 warps) --------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;          // TMEM lanes a warp may read: 32 * (warp id % 4)
+    const int half = ew >> 2;              // which of the two warps of this quarter
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t lead_tmem_empty0 = (CG == 2) ? ptx::mapa(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool red_sum = (p.red_kinds & (FUSEML_RED_SUM | FUSEML_RED_MEAN)) != 0;
+    const bool red_max = (p.red_kinds & FUSEML_RED_MAX) != 0;
+    const bool red_any = red_sum || red_max;
+    float all_sum = 0.0f, all_max = -INFINITY;
+    bool ok = true;
+    for (int32_t t = unit; t < p.num_tiles; t += num_units) {
+      int32_t tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
+      const int32_t tm128 = tm * CG + static_cast<int32_t>(cta_rank);   // index of this CTA's 128-row block
+      const int32_t m = tm128 * kTileM + quarter * 32 + lane;
+      const int32_t n_tile0 = tn * BN;
+      const bool row_ok = m < p.M;
+      if (half == 0) prefetch_operands(p, m, n_tile0, BN, row_ok, lane);
+      // After a failed wait the warp keeps walking its tiles without touching TMEM, so that the
+      // named barriers below still see all eight warps.
+      if (ok && !ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kWhereEpilogueTmemFull)) {
+        ok = false;
+      }
+      ptx::tc_fence_after_sync();
+      float row_sum = 0.0f, row_max = -INFINITY;
+#pragma unroll 1
+      for (int c = half; ok && c < BN / kChunkN; c += kEpiSplit) {
+        const int32_t n0 = n_tile0 + c * kChunkN;
+        if (n0 >= p.N) break;  // uniform across the warp
+        uint32_t r[kChunkN];
+        ptx::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(acc * BN + c * kChunkN), r);
+        ptx::tmem_ld_wait();
+        float v[kChunkN];
+#pragma unroll
+        for (int i = 0; i < kChunkN; ++i) v[i] = __uint_as_float(r[i]);
+        epi::run_program<USES_SAVED>(p, m, n0, row_ok, v);
+        if (p.d != nullptr && row_ok) {
+          epi::store_chunk(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
+        }
+        if (red_any) {
+          if (p.red_axis == FUSEML_AXIS_M) {
+            float vs[kChunkN], vm[kChunkN];
+#pragma unroll
+            for (int i = 0; i < kChunkN; ++i) {
+              vs[i] = row_ok ? v[i] : 0.0f;
+              vm[i] = row_ok ? v[i] : -INFINITY;
+            }
+            if (red_sum) colred[(quarter * 2 + 0) * BN + c * kChunkN + lane] = warp_column_reduce<false>(vs, lane);
+            if (red_max) colred[(quarter * 2 + 1) * BN + c * kChunkN + lane] = warp_column_reduce<true>(vm, lane);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kChunkN; ++i) {
+              const bool in = (n0 + i < p.N);
+              row_sum += in ? v[i] : 0.0f;
+              row_max = in ? fmaxf(row_max, v[i]) : row_max;
+            }
+          }
+        }
+      }
+      // accumulator drained: hand the TMEM buffer back to the (leader's) MMA thread
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0 && ok) {
+        if (CG == 2) ptx::mbar_arrive_cluster(lead_tmem_empty0 + 8u * acc);
+        else ptx::mbar_arrive(tmem_empty_bar(acc));
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+
+      if (red_any) {
+        if (p.red_axis == FUSEML_AXIS_N) {
+          // two warps share a row: each writes its own partial slot
+          if (row_ok && ok) {
+            const int64_t o = (static_cast<int64_t>(tn) * kEpiSplit + half) * p.M + m;
+            if (red_sum) p.red_sum[o] = row_sum;
+            if (red_max) p.red_max[o] = row_max;
+          }
+        } else if (p.red_axis == FUSEML_AXIS_ALL) {
+          if (row_ok) {
+            all_sum += row_sum;
+            all_max = fmaxf(all_max, row_max);
+          }
+        } else {
+          // AXIS_M: combine the four quarters' column partials, one thread per column
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+          for (int j = threadIdx.x - 64; j < BN; j += kEpiWarps * 32) {
+            const int32_t n = n_tile0 + j;
+            if (n < p.N && ok && tm128 * kTileM < p.M) {
+              const int64_t o = static_cast<int64_t>(tm128) * p.N + n;
+              if (red_sum)
+                p.red_sum[o] = colred[0 * BN + j] + colred[2 * BN + j] + colred[4 * BN + j] + colred[6 * BN + j];
+              if (red_max)
+                p.red_max[o] = fmaxf(fmaxf(colred[1 * BN + j], colred[3 * BN + j]),
+                                     fmaxf(colred[5 * BN + j], colred[7 * BN + j]));
+            }
+          }
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+      }
+    }
+    if (red_any && p.red_axis == FUSEML_AXIS_ALL) {
+      const float ws = warp_sum(all_sum);
+      const float wm = warp_max(all_max);
+      if (lane == 0) {
+        colred[ew * 2 + 0] = ws;
+        colred[ew * 2 + 1] = wm;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x == 64) {
+        float s = 0.0f, mx = -INFINITY;
+        for (int w = 0; w < kEpiWarps; ++w) { s += colred[w * 2]; mx = fmaxf(mx, colred[w * 2 + 1]); }
+        if (red_sum) p.red_sum[blockIdx.x] = s;
+        if (red_max) p.red_max[blockIdx.x] = mx;
+      }
+    }
+  }
+
+  // ------------------------------ tear-down ---------------------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (CG == 2) {   // neither CTA may leave while its partner can still touch its memory
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    if (CG == 2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols); else ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace v2
+}  // namespace fuseml

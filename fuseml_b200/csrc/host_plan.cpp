@@ -162,7 +162,7 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
 
   // Candidate tile widths; pick the one with the smaller estimated time
   // (per-tile tensor time x waves, against the HBM time).
-  const int64_t tiles_m = (d->M + 127) / 128;
+  int64_t tiles_m = (d->M + 127) / 128;
   const double per_sm_rate = tc_rate * 1e12 / std::max(1, props.sm_count);
   const int64_t k_eff = (f32 ? 3 : 1) * d->K;
   const int64_t k_pad = round_up(k_eff, plan->tile_k);
@@ -181,16 +181,25 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
     if (t < best) { best = t; best_bn = bn; }
   }
   plan->tile_n = best_bn;
+  // CTA pairs (cta_group::2): a 256 x 256 tile whose B operand is split between the two CTAs'
+  // shared memories, so each SM ingests 32 KB instead of 48 KB per K block.  Worth it whenever
+  // there is more than one 128-row block to pair up.
+  if (best_bn == 256 && d->M > 128) {
+    plan->cluster = 2;
+    tiles_m = (d->M + 255) / 256;
+  }
+  const int cg = plan->cluster;
   const int64_t tiles_n = (d->N + best_bn - 1) / best_bn;
   const int64_t tiles = tiles_m * tiles_n;
-  plan->grid = static_cast<int32_t>(std::min<int64_t>(tiles, props.sm_count));
-  plan->group_m = static_cast<int32_t>(std::min<int64_t>(8, tiles_m));
+  const int64_t units = std::max(1, props.sm_count / cg);
+  plan->grid = static_cast<int32_t>(std::min<int64_t>(tiles, units) * cg);
+  plan->group_m = static_cast<int32_t>(std::min<int64_t>(cg == 2 ? 4 : 8, tiles_m));
 
-  // Shared memory: ring of (A 16 KB + B tile_n*128 B) stages under the opt-in budget.
-  const int stage_bytes = 128 * 128 + best_bn * 128;
+  // Shared memory: ring of (A 16 KB + this CTA's share of B) stages under the opt-in budget.
+  const int stage_bytes = 128 * 128 + (best_bn / cg) * 128;
   const int fixed = 4 * best_bn * 2 * 4 /* column-reduction scratch */ + 256 /* barriers */ + 1024 /* alignment */;
   int stages = (props.smem_per_block_optin - fixed) / stage_bytes;
-  stages = std::max(2, std::min(stages, best_bn == 256 ? 4 : 6));
+  stages = std::max(2, std::min(stages, cg == 2 ? 6 : (best_bn == 256 ? 4 : 6)));
   plan->stages = stages;
   plan->smem_bytes = stages * stage_bytes + fixed;
   plan->tmem_cols = 2 * best_bn;
@@ -218,10 +227,11 @@ void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, Wo
     off += align256(d->N * ld * 4);
   }
   if (d->reduce.kinds != 0) {
-    const int64_t tiles_m = (d->M + plan->tile_m - 1) / plan->tile_m;
+    const int64_t tiles_m = (d->M + plan->tile_m - 1) / plan->tile_m;   // 128-row blocks
     const int64_t tiles_n = (d->N + plan->tile_n - 1) / plan->tile_n;
     int64_t partials, len;
-    if (d->reduce.axis == FUSEML_AXIS_N) { partials = tiles_n; len = d->M; }
+    // per row: one partial per column tile and per epilogue warp sharing the row (two)
+    if (d->reduce.axis == FUSEML_AXIS_N) { partials = tiles_n * 2; len = d->M; }
     else if (d->reduce.axis == FUSEML_AXIS_M) { partials = tiles_m; len = d->N; }
     else { partials = plan->grid; len = 1; }
     w->partials = partials;

@@ -97,11 +97,12 @@ def _plan(native_lib, d, props=None):
 
 
 def test_plan_budgets_and_bounds(native_lib):
-    # compute-bound MLP GEMM: tensor-bound, 256-wide tiles, 4 stages, both TMEM buffers
+    # compute-bound MLP GEMM: tensor-bound, CTA pairs on 256 x 256 tiles, 6 stages of 32 KB per
+    # CTA, both TMEM buffers
     rc, p = _plan(native_lib, _desc(8192, 16384, 4096))
     assert rc == N.OK and p.fuse == 1
-    assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
-    assert p.stages == 4 and p.tmem_cols == 512 and p.acc_stages == 2
+    assert (p.tile_m, p.tile_n, p.tile_k, p.cluster) == (128, 256, 64, 2)
+    assert p.stages == 6 and p.tmem_cols == 512 and p.acc_stages == 2
     assert p.smem_bytes <= 232448
     assert p.grid == 148 and p.bound == 1
     assert p.flops == 2.0 * 8192 * 16384 * 4096
@@ -111,7 +112,7 @@ def test_plan_budgets_and_bounds(native_lib):
     assert rc == N.OK and p.bound == 0 and p.t_hbm_us > p.t_tensor_us
     # tiny problem: latency-bound, still fused (single tier: no bypass)
     rc, p = _plan(native_lib, _desc(128, 512, 2048))
-    assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.grid <= 4 * 2
+    assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.grid <= 4 * 2 and p.cluster == 1
 
 
 def test_plan_follows_device_props(native_lib):
@@ -123,7 +124,7 @@ def test_plan_follows_device_props(native_lib):
     assert rc == N.OK and p.grid == 64
     props.smem_per_block_optin = 120 * 1024
     rc, p = _plan(native_lib, _desc(8192, 16384, 4096), props)
-    assert p.stages == 2 and p.smem_bytes <= 120 * 1024
+    assert p.stages == 3 and p.smem_bytes <= 120 * 1024
 
 
 def test_plan_reports_unsupported_layout_without_fusing(native_lib):
@@ -141,8 +142,8 @@ def test_workspace_bytes(native_lib):
     d.reduce.axis = N.AXIS_N
     d.reduce.out_max = 0x40000
     d.reduce.out_mean = 0x50000
-    # 16 column tiles x 8192 rows x 4 bytes, two partial arrays
-    assert w(C.byref(d), None) == 2 * 16 * 8192 * 4
+    # 16 column tiles x 2 epilogue warps per row x 8192 rows x 4 bytes, two partial arrays
+    assert w(C.byref(d), None) == 2 * 16 * 2 * 8192 * 4
     d32 = _desc(128, 2048, 512, ab=N.F32)
     ld = 3 * 512
     assert w(C.byref(d32), None) == (128 * ld + 2048 * ld) * 4

@@ -152,7 +152,7 @@ def test_launcher_host_contract():
 
 def test_launch_params_and_tile_chooser():
     lp = F.compute_launch_params(8192, 16384, 4096, torch.bfloat16)
-    assert (lp.block_m, lp.block_n, lp.block_k, lp.num_stages) == (128, 256, 64, 4)
+    assert (lp.block_m, lp.block_n, lp.block_k, lp.num_stages) == (128, 256, 64, 6)
     assert F.compute_sram_bytes(128, 256, 64, 2, 4) == 4 * (16384 + 32768)
     tuner = F.SRAMAutotuner()
     cfg = tuner.get_best_config(8192, 16384, 4096, torch.bfloat16)
