@@ -99,3 +99,30 @@ def test_fp32_reductions_keep_fp32(native_lib):
     assert ((s.double() - rs).abs().max() / rs.abs().max()).item() < 1e-3
     assert ((m.double() - rm).abs().max()).item() < 1e-3
     torch._dynamo.reset()
+
+
+def test_host_streamed_runtime_matches_direct_call(native_lib):
+    """Row chunks through three CUDA streams give the same bytes as one direct call."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+    from fuseml_b200.runtime import HostStreamedModule
+
+    torch._dynamo.reset()
+    case, module, args = _cuda_case("cfg4")
+    rows, d = 1024, case.sizes["D"]
+    compiled = torch.compile(module, backend=F.FuseMLCompiler())
+    g = torch.Generator().manual_seed(7)
+    x_host = torch.randn(rows, d, generator=g).to(torch.bfloat16).pin_memory()
+    y_host = torch.zeros(rows, d, dtype=torch.bfloat16).pin_memory()
+    runner = HostStreamedModule(compiled, rows_per_chunk=256)
+    for _ in range(3):                       # batches pipeline into each other
+        runner.submit(x_host, y_host)
+    runner.synchronize()
+    with torch.no_grad():
+        ref = compiled(x_host.cuda()).cpu()
+    assert torch.equal(y_host, ref)
+    assert runner.h2d_bytes == 3 * rows * d * 2 and runner.d2h_bytes == 3 * rows * d * 2
+    with pytest.raises(ValueError):
+        runner.submit(torch.zeros(4, d, dtype=torch.bfloat16), y_host)     # not pinned
+    torch._dynamo.reset()
