@@ -141,7 +141,9 @@ def load(path: os.PathLike | str | None = None) -> C.CDLL:
     with _lock:
         if _lib is not None and path is None:
             return _lib
-        p = Path(path) if path is not None else LIB_PATH
+        # FUSEML_SM100_LIB points at an alternative build of the same ABI (A/B measurements)
+        override = os.environ.get("FUSEML_SM100_LIB")
+        p = Path(path) if path is not None else (Path(override) if override else LIB_PATH)
         if not p.exists():
             raise NativeLibraryError(
                 f"{p} is missing: build it with `python -m fuseml_b200.build` "

@@ -15,15 +15,29 @@
 namespace fuseml {
 namespace epi {
 
+// 1 + erf(z) without cancellation for negative z: Abramowitz-Stegun 7.1.26 gives
+// erfc(|z|) = poly(t) * exp(-z^2), t = 1/(1 + p|z|), |error| < 1.5e-7; then
+// 1 + erf(z) = erfc(|z|) for z < 0 and 2 - erfc(|z|) otherwise.  Two special-function-unit
+// ops and six FMAs per element, no divergent branch (erff() costs about three times as much).
+__device__ __forceinline__ float one_plus_erf(float z) {
+  const float a = fabsf(z);
+  const float t = __frcp_rn(fmaf(0.3275911f, a, 1.0f));
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erfc_a = poly * t * __expf(-a * a);
+  return z < 0.0f ? erfc_a : 2.0f - erfc_a;
+}
 __device__ __forceinline__ float gelu_erf(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+  return 0.5f * x * one_plus_erf(x * 0.70710678118654752440f);
 }
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   const float u = k0 * (x + k1 * x * x * x);
   return 0.5f * x * (1.0f + tanhf(u));
 }
-__device__ __forceinline__ float sigmoid(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 __device__ __forceinline__ float load_scalar(const void* p, int64_t idx, int32_t dtype) {
   if (dtype == FUSEML_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
