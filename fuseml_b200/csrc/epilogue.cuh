@@ -21,7 +21,7 @@ namespace epi {
 // ops and six FMAs per element, no divergent branch (erff() costs about three times as much).
 __device__ __forceinline__ float one_plus_erf(float z) {
   const float a = fabsf(z);
-  const float t = __frcp_rn(fmaf(0.3275911f, a, 1.0f));
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, a, 1.0f));  // MUFU.RCP (an IEEE-rounded reciprocal costs several times more)
   float poly = fmaf(t, 1.061405429f, -1.453152027f);
   poly = fmaf(poly, t, 1.421413741f);
   poly = fmaf(poly, t, -0.284496736f);
@@ -45,11 +45,20 @@ __device__ __forceinline__ float load_scalar(const void* p, int64_t idx, int32_t
   return reinterpret_cast<const float*>(p)[idx];
 }
 
-// Loads operand[m, n0 .. n0+31] into t[].  Columns >= N read as 0.  The fast
-// path (unit column stride, 16-byte aligned, full chunk) uses 128-bit loads;
-// with stride_m == 0 all lanes hit the same address and the load broadcasts.
-__device__ __forceinline__ void load_operand_chunk(const EpiOperand& o, int64_t m, int32_t n0, int32_t N,
-                                                   float (&t)[kChunkN]) {
+// v[i] = combine(v[i], operand[m, n0 + i]) for the 32 columns of a chunk, without a 32-element
+// temporary: values are folded in as each 16-byte word is unpacked.  combine is a*b for MUL and
+// sa*a + sb*b otherwise (ADD: 1,1; SUB: 1,-1; RSUB: -1,1).  Columns >= N are left alone.  The
+// fast path (unit column stride, 16-byte aligned, full chunk) uses 128-bit loads; with
+// stride_m == 0 all lanes hit the same address and the load broadcasts.
+__device__ __forceinline__ float combine(bool mul, float sa, float sb, float a, float b) {
+  return mul ? a * b : fmaf(sb, b, sa * a);
+}
+
+__device__ __forceinline__ void fold_operand_chunk(float (&v)[kChunkN], int32_t code, const EpiOperand& o, int64_t m,
+                                                   int32_t n0, int32_t N) {
+  const bool mul = code == FUSEML_OP_MUL_T;
+  const float sa = code == FUSEML_OP_RSUB_T ? -1.0f : 1.0f;
+  const float sb = code == FUSEML_OP_SUB_T ? -1.0f : 1.0f;
   const int64_t base = m * o.stride_m + static_cast<int64_t>(n0) * o.stride_n;
   const bool full = (n0 + kChunkN <= N);
   if (o.stride_n == 1 && full) {
@@ -59,7 +68,10 @@ __device__ __forceinline__ void load_operand_chunk(const EpiOperand& o, int64_t 
 #pragma unroll
         for (int i = 0; i < kChunkN / 4; ++i) {
           const float4 q = __ldg(reinterpret_cast<const float4*>(p) + i);
-          t[4 * i + 0] = q.x; t[4 * i + 1] = q.y; t[4 * i + 2] = q.z; t[4 * i + 3] = q.w;
+          v[4 * i + 0] = combine(mul, sa, sb, v[4 * i + 0], q.x);
+          v[4 * i + 1] = combine(mul, sa, sb, v[4 * i + 1], q.y);
+          v[4 * i + 2] = combine(mul, sa, sb, v[4 * i + 2], q.z);
+          v[4 * i + 3] = combine(mul, sa, sb, v[4 * i + 3], q.w);
         }
         return;
       }
@@ -72,13 +84,11 @@ __device__ __forceinline__ void load_operand_chunk(const EpiOperand& o, int64_t 
           const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            if (o.dtype == FUSEML_BF16) {
-              const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
-              t[8 * i + 2 * j] = f.x; t[8 * i + 2 * j + 1] = f.y;
-            } else {
-              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-              t[8 * i + 2 * j] = f.x; t[8 * i + 2 * j + 1] = f.y;
-            }
+            float2 f;
+            if (o.dtype == FUSEML_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+            else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            v[8 * i + 2 * j] = combine(mul, sa, sb, v[8 * i + 2 * j], f.x);
+            v[8 * i + 2 * j + 1] = combine(mul, sa, sb, v[8 * i + 2 * j + 1], f.y);
           }
         }
         return;
@@ -87,7 +97,22 @@ __device__ __forceinline__ void load_operand_chunk(const EpiOperand& o, int64_t 
   }
 #pragma unroll
   for (int i = 0; i < kChunkN; ++i) {
-    t[i] = (n0 + i < N) ? load_scalar(o.ptr, base + static_cast<int64_t>(i) * o.stride_n, o.dtype) : 0.0f;
+    if (n0 + i < N)
+      v[i] = combine(mul, sa, sb, v[i], load_scalar(o.ptr, base + static_cast<int64_t>(i) * o.stride_n, o.dtype));
+  }
+}
+
+// v[i] (+|*)= src[i], src = 32 fp32 values staged in shared memory (same address for every
+// lane: the reads broadcast)
+template <bool kMul>
+__device__ __forceinline__ void fold_staged(float (&v)[kChunkN], const float* src) {
+#pragma unroll
+  for (int i = 0; i < kChunkN / 4; ++i) {
+    const float4 q = reinterpret_cast<const float4*>(src)[i];
+    v[4 * i + 0] = kMul ? v[4 * i + 0] * q.x : v[4 * i + 0] + q.x;
+    v[4 * i + 1] = kMul ? v[4 * i + 1] * q.y : v[4 * i + 1] + q.y;
+    v[4 * i + 2] = kMul ? v[4 * i + 2] * q.z : v[4 * i + 2] + q.z;
+    v[4 * i + 3] = kMul ? v[4 * i + 3] * q.w : v[4 * i + 3] + q.w;
   }
 }
 
@@ -143,9 +168,11 @@ __device__ __forceinline__ void store_chunk(void* base_ptr, int64_t row_off, int
 
 // Runs the program on one chunk.  `row_ok` is false for rows past M: their
 // operand loads and aux stores are skipped (values are don't-care).
+// `staged` points at this chunk's 32 columns of the row vectors staged in shared memory
+// (vector j at staged + j * staged_stride).
 template <bool kUsesSaved>
 __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int32_t n0, bool row_ok,
-                                            float (&v)[kChunkN]) {
+                                            float (&v)[kChunkN], const float* staged, int32_t staged_stride) {
   float s[kUsesSaved ? kChunkN : 1];
   if (kUsesSaved) {
 #pragma unroll
@@ -184,22 +211,12 @@ __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int3
       case FUSEML_OP_MUL_T:
       case FUSEML_OP_SUB_T:
       case FUSEML_OP_RSUB_T: {
-        if (row_ok) {
-          float t[kChunkN];
-          load_operand_chunk(p.operands[p.ops[op].slot], m, n0, p.N, t);
-          if (code == FUSEML_OP_ADD_T) {
-#pragma unroll
-            for (int i = 0; i < kChunkN; ++i) v[i] += t[i];
-          } else if (code == FUSEML_OP_MUL_T) {
-#pragma unroll
-            for (int i = 0; i < kChunkN; ++i) v[i] *= t[i];
-          } else if (code == FUSEML_OP_SUB_T) {
-#pragma unroll
-            for (int i = 0; i < kChunkN; ++i) v[i] -= t[i];
-          } else {
-#pragma unroll
-            for (int i = 0; i < kChunkN; ++i) v[i] = t[i] - v[i];
-          }
+        const int32_t pre = p.ops[op].reserved;
+        if (pre == 1 || pre == 2) {
+          const float* src = staged + (pre - 1) * staged_stride;
+          if (code == FUSEML_OP_ADD_T) fold_staged<false>(v, src); else fold_staged<true>(v, src);
+        } else if (row_ok) {
+          fold_operand_chunk(v, code, p.operands[p.ops[op].slot], m, n0, p.N);
         }
       } break;
       case FUSEML_OP_STORE_AUX: {

@@ -284,6 +284,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   p.n_ops = desc->n_ops;
   for (int i = 0; i < desc->n_ops; ++i) {
     p.ops[i] = desc->ops[i];
+    p.ops[i].reserved = 0;
     const int32_t oc = desc->ops[i].opcode;
     if (oc == FUSEML_OP_SAVE || oc == FUSEML_OP_SWAP || oc == FUSEML_OP_ADD_SAVED || oc == FUSEML_OP_MUL_SAVED)
       p.uses_saved = 1;
@@ -294,6 +295,34 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     p.operands[i].stride_n = desc->operands[i].stride_n;
     p.operands[i].dtype = desc->operands[i].dtype;
   }
+  // operands fetched ahead of use (see GemmParams): row vectors staged in shared memory, the
+  // first 16-byte-loadable 16-bit matrix operand requested at the top of each chunk
+  p.vec_slot[0] = p.vec_slot[1] = -1;
+  p.mat_slot = -1;
+  {
+    int n_vec = 0;
+    for (int i = 0; i < desc->n_ops; ++i) {
+      const int32_t oc = desc->ops[i].opcode;
+      if (oc != FUSEML_OP_ADD_T && oc != FUSEML_OP_MUL_T) continue;
+      const int32_t slot = desc->ops[i].slot;
+      const fuseml_operand_t& o = desc->operands[slot];
+      if (o.stride_m == 0 && o.stride_n == 1) {
+        int idx = -1;
+        for (int j = 0; j < n_vec; ++j) if (p.vec_slot[j] == slot) idx = j;
+        if (idx < 0 && n_vec < 2) { idx = n_vec; p.vec_slot[n_vec++] = slot; }
+        if (idx >= 0) p.ops[i].reserved = idx + 1;
+      } else if (o.stride_n == 1 && (o.dtype == FUSEML_BF16 || o.dtype == FUSEML_F16) &&
+                 (reinterpret_cast<uintptr_t>(o.ptr) & 15u) == 0 && (o.stride_m * 2) % 16 == 0 &&
+                 (p.mat_slot < 0 || p.mat_slot == slot)) {
+        p.mat_slot = slot;
+        p.ops[i].reserved = 3;
+      }
+    }
+  }
+  // an operand whose every element is read by at most two tile units is a pure stream
+  p.a_stream = p.b_stream = 0;
+  if (p.tiles_m <= 2 && p.tiles_n > 2) { p.b_stream = 1; p.a_stream = 2; }
+  else if (p.tiles_n <= 2 && p.tiles_m > 2) { p.a_stream = 1; p.b_stream = 2; }
   p.red_kinds = desc->reduce.kinds;
   p.red_axis = desc->reduce.axis;
   if (desc->reduce.kinds != 0) {

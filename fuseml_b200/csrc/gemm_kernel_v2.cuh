@@ -41,7 +41,8 @@ struct Smem {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kRingBytes = STAGES * kStageBytes;
   static constexpr int kColRedBytes = 4 * 2 * BN * 4;             // [quarter][sum|max][BN]
-  static constexpr int kBarOffset = kRingBytes + kColRedBytes;
+  static constexpr int kStagedBytes = 2 * 2 * BN * 4;             // [acc buffer][row vector][BN] fp32
+  static constexpr int kBarOffset = kRingBytes + kColRedBytes + kStagedBytes;
   static constexpr int kNumBars = 2 * STAGES + 4;
   static constexpr int kTotalBytes = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kDynamicBytes = kTotalBytes + 1024;
@@ -129,6 +130,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   float* colred = reinterpret_cast<float*>(smem + L::kRingBytes);
+  float* staged_base = reinterpret_cast<float*>(smem + L::kRingBytes + L::kColRedBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -178,6 +180,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       int stage = 0;
       uint32_t phase = 0, issued = 0;
       bool ok = true;
+      const uint64_t pol_stream = ptx::policy_evict_first();
+      const uint64_t pol_keep = ptx::policy_evict_last();
       for (int32_t t = unit; t < p.num_tiles && ok; t += num_units) {
         int32_t tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
@@ -190,28 +194,29 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           }
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
           const uint32_t b_dst = a_dst + L::kABytes;
-          if (CG == 1) {
-            ptx::mbar_arrive_expect_tx(full_bar(stage), L::kStageBytes);
-            ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * BK, m0);
-            if (!B_MN) {
-              ptx::tma_load_2d(b_dst, &tmap_b, full_bar(stage), kb * BK, n0);
+          // one load helper for both modes: completion bytes go to `bar` (for a pair: the
+          // leader's barrier, addressed through the cluster window)
+          const uint32_t bar = (CG == 2) ? ptx::mapa(full_bar(stage), 0) : full_bar(stage);
+          if (CG == 1 || is_leader) ptx::mbar_arrive_expect_tx(full_bar(stage), CG * L::kStageBytes);
+          // policy: 0 = default, 1 = evict-first (pure stream), 2 = evict-last (keep resident)
+          auto load = [&](uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, int32_t policy) {
+            if (CG == 2) {
+              if (policy == 1) ptx::tma_load_2d_pair_hint(dst, tm, bar, c0, c1, pol_stream);
+              else if (policy == 2) ptx::tma_load_2d_pair_hint(dst, tm, bar, c0, c1, pol_keep);
+              else ptx::tma_load_2d_pair(dst, tm, bar, c0, c1);
             } else {
-#pragma unroll
-              for (int j = 0; j < BN_CTA / 64; ++j)
-                ptx::tma_load_2d(b_dst + j * (BK * kSwizzleBytes), &tmap_b, full_bar(stage), n0 + j * 64, kb * BK);
+              if (policy == 1) ptx::tma_load_2d_hint(dst, tm, bar, c0, c1, pol_stream);
+              else if (policy == 2) ptx::tma_load_2d_hint(dst, tm, bar, c0, c1, pol_keep);
+              else ptx::tma_load_2d(dst, tm, bar, c0, c1);
             }
+          };
+          load(a_dst, &tmap_a, kb * BK, m0, p.a_stream);
+          if (!B_MN) {
+            load(b_dst, &tmap_b, kb * BK, n0, p.b_stream);
           } else {
-            // bytes of both CTAs are counted on the leader's barrier
-            const uint32_t lead_full = ptx::mapa(full_bar(stage), 0);
-            if (is_leader) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * L::kStageBytes);
-            ptx::tma_load_2d_pair(a_dst, &tmap_a, lead_full, kb * BK, m0);
-            if (!B_MN) {
-              ptx::tma_load_2d_pair(b_dst, &tmap_b, lead_full, kb * BK, n0);
-            } else {
 #pragma unroll
-              for (int j = 0; j < BN_CTA / 64; ++j)
-                ptx::tma_load_2d_pair(b_dst + j * (BK * kSwizzleBytes), &tmap_b, lead_full, n0 + j * 64, kb * BK);
-            }
+            for (int j = 0; j < BN_CTA / 64; ++j)
+              load(b_dst + j * (BK * kSwizzleBytes), &tmap_b, n0 + j * 64, kb * BK, p.b_stream);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -309,6 +314,23 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const int32_t n_tile0 = tn * BN;
       const bool row_ok = m < p.M;
       if (half == 0) prefetch_operands(p, m, n_tile0, BN, row_ok, lane);
+      // Row vectors (bias): stage this tile's slice in shared memory as fp32 while the K loop
+      // runs.  Two buffers (by accumulator parity) and one barrier per tile suffice: nobody
+      // passes the next tile's barrier before every warp has finished reading this one.
+      float* staged = staged_base + acc * (2 * BN);
+      if (p.vec_slot[0] >= 0) {
+        const int idx = threadIdx.x - 64;
+        if (idx < BN) {
+          const int32_t n = n_tile0 + idx;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int32_t slot = p.vec_slot[j];
+            if (slot >= 0)
+              staged[j * BN + idx] = n < p.N ? epi::load_scalar(p.operands[slot].ptr, n, p.operands[slot].dtype) : 0.0f;
+          }
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+      }
       // After a failed wait the warp keeps walking its tiles without touching TMEM, so that the
       // named barriers below still see all eight warps.
       if (ok && !ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kWhereEpilogueTmemFull)) {
@@ -320,13 +342,25 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       for (int c = half; ok && c < BN / kChunkN; c += kEpiSplit) {
         const int32_t n0 = n_tile0 + c * kChunkN;
         if (n0 >= p.N) break;  // uniform across the warp
+        // Pull this thread's 64-byte slices of the matrix operand (residual) for this chunk and
+        // for the warp's next one into L1 now: by the time the program reaches the op, the
+        // load hits L1 instead of waiting on L2.  Costs no registers.
+        if (p.mat_slot >= 0 && row_ok) {
+          const EpiOperand& mo = p.operands[p.mat_slot];
+          const char* mp = reinterpret_cast<const char*>(mo.ptr) + (static_cast<int64_t>(m) * mo.stride_m + n0) * 2;
+          if (c == half) { ptx::prefetch_l1(mp); ptx::prefetch_l1(mp + 63); }
+          if (n0 + kEpiSplit * kChunkN < p.N) {
+            ptx::prefetch_l1(mp + kEpiSplit * kChunkN * 2);
+            ptx::prefetch_l1(mp + kEpiSplit * kChunkN * 2 + 63);
+          }
+        }
         uint32_t r[kChunkN];
         ptx::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(acc * BN + c * kChunkN), r);
         ptx::tmem_ld_wait();
         float v[kChunkN];
 #pragma unroll
         for (int i = 0; i < kChunkN; ++i) v[i] = __uint_as_float(r[i]);
-        epi::run_program<USES_SAVED>(p, m, n0, row_ok, v);
+        epi::run_program<USES_SAVED>(p, m, n0, row_ok, v, staged + c * kChunkN, BN);
         if (p.d != nullptr && row_ok) {
           epi::store_chunk(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
         }

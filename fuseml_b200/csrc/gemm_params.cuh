@@ -40,6 +40,17 @@ struct GemmParams {
   float* red_sum;    // [partials][len]
   float* red_max;    // [partials][len]
   int32_t uses_saved;  // program contains SAVE/SWAP/*_SAVED
+  // Operand fetch ahead of use (ops[i].reserved selects the path: 0 = load where the op runs):
+  //   vec_slot[j] (reserved = 1 + j): a row vector (bias) - its slice for the tile is staged in
+  //     shared memory as fp32 once per tile, while the K loop is still running;
+  //   mat_slot (reserved = 3): a full [M,N] 16-bit operand (residual) - each thread's 64-byte
+  //     slices are prefetched into L1 one chunk ahead of their use.
+  int32_t vec_slot[2];
+  int32_t mat_slot;
+  // L2 policy of the operand loads: 0 = default, 1 = evict-first (an operand every element of
+  // which is read by one or two tiles only: keeping it would push reusable data out of L2),
+  // 2 = evict-last (the small operand everybody re-reads while the other one streams past)
+  int32_t a_stream, b_stream;
   int32_t* status;     // device status word (bounded-wait time-outs)
 };
 
