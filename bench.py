@@ -171,11 +171,9 @@ class MLPBlock(Workload):
             return out
         y, s, m = out
         if self.world > 1:
-            import torch.distributed as dist
+            from fuseml_b200.sharding import allreduce_scalars
 
-            s, m = s.float(), m.float()
-            dist.all_reduce(s, op=dist.ReduceOp.SUM)
-            dist.all_reduce(m, op=dist.ReduceOp.MAX)
+            s, m = allreduce_scalars(total=s, maximum=m)     # NCCL all-reduce: SUM and MAX of one scalar each
         self.scalars = (s, m)
         return y
 
