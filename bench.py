@@ -137,6 +137,10 @@ class Workload:
     def e2e_finish(self):
         """Called once after the last e2e step, before the closing event is recorded."""
 
+    def use_graphs(self):
+        """Capture the resident step in CUDA graphs where that pays (launch-bound steps)."""
+        return False
+
 
 class MLPBlock(Workload):
     """cfg4 (blocks=1) and cfg5 (blocks=4 + global sum/amax [+ allreduce])."""
@@ -221,6 +225,7 @@ class ActHeavyGemm(Workload):
         self.x, self.r = self.x_host.cuda(), self.r_host.cuda()
         self.x_in, self.r_in = torch.empty_like(self.x), torch.empty_like(self.r)
         self.i = 0
+        self.graphs = None
         self.tokens = rows
         self.flops_per_launch = self.flops = 2.0 * rows * Kd * Nn
         self.algo_bytes = 2.0 * (rows * Kd + Kd * Nn + Nn + 2 * rows * Nn)
@@ -235,7 +240,23 @@ class ActHeavyGemm(Workload):
             return self.compiled(x, r)
 
     def step(self):
+        if self.graphs is not None:
+            g = self.graphs[self.i % len(self.graphs)]
+            self.i += 1
+            return g()
         return self._forward(self.x, self.r)
+
+    def use_graphs(self):
+        """One captured graph per weight copy (the step is a single ~50 us kernel: without a
+        graph the host's launch path is part of the measurement)."""
+        from fuseml_b200.runtime import GraphedCallable
+
+        graphs = []
+        for W in self.Ws:
+            self.module.W.data = W
+            graphs.append(GraphedCallable(self.compiled, self.x, self.r))
+        self.graphs = graphs
+        return True
 
     def e2e_step(self):
         self.x_in.copy_(self.x_host, non_blocking=True)
@@ -436,6 +457,7 @@ def main():
     ap.add_argument("--workload", default="cfg4", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="do not capture launch-bound steps in CUDA graphs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -490,11 +512,22 @@ def main():
     for _ in range(W):
         wl.step()
     wl.check_compiled()
+    graphed = False
+    if not args.no_graph:
+        try:
+            graphed = wl.use_graphs()
+        except Exception as exc:          # capture is an optimisation, never a requirement
+            print(f"[bench] CUDA graph capture failed, stepping eagerly: {exc!r}", file=sys.stderr)
+            wl.graphs = None
+        for _ in range(3):
+            wl.step()
     if rank == 0:
         sampler.wait_for_samples(1)     # started before the workload was built; normally no wait
     launches_before = wl.fused_launches()
     total_ms = timed(wl.step, steps)
     launches_timed = wl.fused_launches() - launches_before
+    if graphed:
+        launches_timed = wl.gemm_launches_per_step * steps     # replays do not pass through the Python counters
     # The timed region may be shorter than one sampling period (50 ms): repeat the same step,
     # untimed, so that the window under load is at least 0.4 s.  The count is derived from the
     # all-reduced time, so every rank runs the same number of steps (and collectives).
@@ -544,7 +577,8 @@ def main():
         "config": {"workload": wl.name, "rows_per_gpu": wl.tokens, "global_rows": wl.tokens * world,
                    "l2": "inputs larger than L2 (weights + activations per step exceed 126 MB"
                          + ("; weight copies rotated)" if args.workload == "cfg2" else ")"),
-                   "parallelism": f"rows sharded over {world} GPU(s), weights replicated"},
+                   "parallelism": f"rows sharded over {world} GPU(s), weights replicated",
+                   "cuda_graph": bool(graphed)},
         "e2e": {"value": wl.tokens * world / (e2e_ms / steps * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes, "ms_per_step": e2e_ms / steps},
         "gpu_launches": launches_timed + (steps if wl.launches_per_step > wl.gemm_launches_per_step else 0),

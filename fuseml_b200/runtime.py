@@ -1,4 +1,6 @@
-"""Row-streamed execution from host memory on CUDA streams.
+"""Stream- and graph-level runtime around a compiled forward: CUDA-graph replay for
+launch-bound chains (:class:`GraphedCallable`) and row-streamed execution from pinned host
+memory on three CUDA streams (:class:`HostStreamedModule`).
 
 Every chain this package fuses is independent per row of the activation matrix (that is
 also why rows can be sharded over GPUs with no collective).  When the activations start
@@ -22,6 +24,37 @@ from __future__ import annotations
 from typing import Callable, Sequence
 
 import torch
+
+
+class GraphedCallable:
+    """A fused forward captured once in a CUDA graph and replayed.
+
+    Chains of microsecond-scale kernels are bound by the host's launch path (Python, the
+    descriptor fill, the driver call); a captured graph replays the same launches with one
+    driver call.  Launchers allocate their outputs through torch, which is capturable: the
+    outputs live in the graph's private pool and are overwritten by every replay.
+
+    ``fn`` is called with ``args`` (static device tensors: update them in place, then replay).
+    The first calls run eagerly on a side stream (kernel attributes and symbol look-ups happen
+    there, outside the capture).
+    """
+
+    def __init__(self, fn: Callable, *args: torch.Tensor, warmup: int = 3) -> None:
+        self.args = args
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(max(1, warmup)):
+                fn(*args)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.outputs = fn(*args)
+
+    def __call__(self):
+        self.graph.replay()
+        return self.outputs
 
 
 class HostStreamedModule:
