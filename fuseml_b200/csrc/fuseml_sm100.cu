@@ -126,10 +126,10 @@ static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPar
 
 static int check_plan(const fuseml_plan_t* pl) {
   if (pl->tile_m != 128) return FUSEML_E_PLAN;
-  if (pl->tile_n != 128 && pl->tile_n != 256) return FUSEML_E_PLAN;
+  if (pl->tile_n < 32 || pl->tile_n > 256 || pl->tile_n % 32 != 0) return FUSEML_E_PLAN;
   if (pl->grid <= 0 || pl->group_m <= 0) return FUSEML_E_PLAN;
   if (pl->cluster != 1 && pl->cluster != 2) return FUSEML_E_PLAN;
-  if (pl->cluster == 2 && pl->tile_n != 256) return FUSEML_E_PLAN;
+  if (pl->cluster == 2 && pl->tile_n <= 128) return FUSEML_E_PLAN;
   return FUSEML_OK;
 }
 
@@ -256,7 +256,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     a_ptr = a2; b_ptr = b2; K = 3 * desc->K; lda = ld; ldb = ld; b_mn = false;
   }
 
-  const int BN = plan.tile_n;
+  const int BN = plan.tile_n;          // run-time tile width; kernels are built for 128 and 256
   const int BK = f32 ? 32 : 64;
   CUtensorMap ta, tb;
   rc = encode_2d(&ta, desc->ab_dtype, a_ptr, desc->M, K, lda, BK, kTileM);
@@ -276,6 +276,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   p.tiles_m = static_cast<int32_t>((desc->M + kTileM * CGr - 1) / (kTileM * CGr));
   p.tiles_n = static_cast<int32_t>((desc->N + BN - 1) / BN);
   p.num_tiles = p.tiles_m * p.tiles_n;
+  p.bn = BN;
   p.group_m = std::min(plan.group_m, p.tiles_m);
   p.num_kb = static_cast<int32_t>((K + BK - 1) / BK);
   p.d = desc->d;
@@ -341,7 +342,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     fill_neutral_kernel<<<1, 256, 0, stream>>>(p.red_sum, p.red_max, static_cast<int>(w.partials));
   }
   if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, p, fmt, b_mn, grid, stream);
-  else if (BN == 256) rc = launch_bn<256, 4, 1>(ta, tb, p, fmt, b_mn, grid, stream);
+  else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, p, fmt, b_mn, grid, stream);
   else rc = launch_bn<128, 6, 1>(ta, tb, p, fmt, b_mn, grid, stream);
   if (rc != FUSEML_OK) return rc;
 

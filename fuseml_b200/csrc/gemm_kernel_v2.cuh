@@ -112,7 +112,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   constexpr int BK = kSwizzleBytes / kElemBytes;
   constexpr int UMMA_K = 32 / kElemBytes;
   constexpr int kKSteps = BK / UMMA_K;
-  constexpr int BN_CTA = BN / CG;                 // B columns this CTA loads
+  constexpr int BN_CTA = BN / CG;                 // most B columns one CTA loads (sizes shared memory)
   constexpr uint32_t kTmemCols = 2 * BN;
   static_assert(!(B_MN && FMT == 2), "MN-major B is only wired for 16-bit operands");
   static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair");
@@ -173,6 +173,12 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_base_slot;
   const int32_t num_kb = p.num_kb;
+  // The tile width is a run-time value (a multiple of 32, at most BN): the router may shave it
+  // so that the number of tiles fits the number of CTA pairs without a ragged last wave.
+  const int32_t bn = p.bn;
+  const int32_t bn_cta = bn / CG;
+  const int32_t n_boxes = (bn_cta + 63) / 64;                          // MN-major: 64-column TMA boxes
+  const uint32_t stage_tx = L::kABytes + (B_MN ? n_boxes * (BK * kSwizzleBytes) : bn_cta * kSwizzleBytes);
 
   if (warp == 0) {
     // ------------------------------ TMA producer (every CTA) -----------------------------
@@ -186,7 +192,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         int32_t tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
         const int32_t m0 = tm * (kTileM * CG) + static_cast<int32_t>(cta_rank) * kTileM;
-        const int32_t n0 = tn * BN + static_cast<int32_t>(cta_rank) * BN_CTA;
+        const int32_t n0 = tn * bn + static_cast<int32_t>(cta_rank) * bn_cta;
         for (int32_t kb = 0; kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWhereProducerEmpty)) {
             ok = false;
@@ -197,7 +203,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           // one load helper for both modes: completion bytes go to `bar` (for a pair: the
           // leader's barrier, addressed through the cluster window)
           const uint32_t bar = (CG == 2) ? ptx::mapa(full_bar(stage), 0) : full_bar(stage);
-          if (CG == 1 || is_leader) ptx::mbar_arrive_expect_tx(full_bar(stage), CG * L::kStageBytes);
+          if (CG == 1 || is_leader) ptx::mbar_arrive_expect_tx(full_bar(stage), CG * stage_tx);
           // policy: 0 = default, 1 = evict-first (pure stream), 2 = evict-last (keep resident)
           auto load = [&](uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, int32_t policy) {
             if (CG == 2) {
@@ -216,7 +222,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           } else {
 #pragma unroll
             for (int j = 0; j < BN_CTA / 64; ++j)
-              load(b_dst + j * (BK * kSwizzleBytes), &tmap_b, n0 + j * 64, kb * BK, p.b_stream);
+              if (j < n_boxes) load(b_dst + j * (BK * kSwizzleBytes), &tmap_b, n0 + j * 64, kb * BK, p.b_stream);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -245,7 +251,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ---------------------------
     if (lane == 0 && is_leader) {
-      constexpr uint32_t idesc = ptx::make_idesc(FMT, 0u, B_MN ? 1u : 0u, kTileM * CG, BN);
+      const uint32_t idesc = ptx::make_idesc(FMT, 0u, B_MN ? 1u : 0u, kTileM * CG, static_cast<uint32_t>(bn));
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -311,16 +317,16 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
       const int32_t tm128 = tm * CG + static_cast<int32_t>(cta_rank);   // index of this CTA's 128-row block
       const int32_t m = tm128 * kTileM + quarter * 32 + lane;
-      const int32_t n_tile0 = tn * BN;
+      const int32_t n_tile0 = tn * bn;
       const bool row_ok = m < p.M;
-      if (half == 0) prefetch_operands(p, m, n_tile0, BN, row_ok, lane);
+      if (half == 0) prefetch_operands(p, m, n_tile0, bn, row_ok, lane);
       // Row vectors (bias): stage this tile's slice in shared memory as fp32 while the K loop
       // runs.  Two buffers (by accumulator parity) and one barrier per tile suffice: nobody
       // passes the next tile's barrier before every warp has finished reading this one.
       float* staged = staged_base + acc * (2 * BN);
       if (p.vec_slot[0] >= 0) {
         const int idx = threadIdx.x - 64;
-        if (idx < BN) {
+        if (idx < bn) {
           const int32_t n = n_tile0 + idx;
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
@@ -339,7 +345,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       ptx::tc_fence_after_sync();
       float row_sum = 0.0f, row_max = -INFINITY;
 #pragma unroll 1
-      for (int c = half; ok && c < BN / kChunkN; c += kEpiSplit) {
+      for (int c = half; ok && c < bn / kChunkN; c += kEpiSplit) {
         const int32_t n0 = n_tile0 + c * kChunkN;
         if (n0 >= p.N) break;  // uniform across the warp
         // Pull this thread's 64-byte slices of the matrix operand (residual) for this chunk and
@@ -410,7 +416,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         } else {
           // AXIS_M: combine the four quarters' column partials, one thread per column
           asm volatile("bar.sync 1, 256;" ::: "memory");
-          for (int j = threadIdx.x - 64; j < BN; j += kEpiWarps * 32) {
+          for (int j = threadIdx.x - 64; j < bn; j += kEpiWarps * 32) {
             const int32_t n = n_tile0 + j;
             if (n < p.N && ok && tm128 * kTileM < p.M) {
               const int64_t o = static_cast<int64_t>(tm128) * p.N + n;

@@ -27,6 +27,7 @@ struct EpiOperand {
 struct GemmParams {
   int32_t M, N, K;
   int32_t tiles_m, tiles_n, num_tiles, group_m, num_kb;
+  int32_t bn;        // tile width actually used (multiple of 32, at most the kernel's BN)
   void* d;           // may be null (reduction-only chains)
   int64_t ldd;
   int32_t out_dtype;

@@ -180,14 +180,24 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
     const double t = std::max(waves * t_tile * (bn == 128 ? 1.05 : 1.0), plan->t_hbm_us);
     if (t < best) { best = t; best_bn = bn; }
   }
-  plan->tile_n = best_bn;
   // CTA pairs (cta_group::2): a 256 x 256 tile whose B operand is split between the two CTAs'
-  // shared memories, so each SM ingests 32 KB instead of 48 KB per K block.  Worth it whenever
-  // there is more than one 128-row block to pair up.
-  if (best_bn == 256 && d->M > 128) {
+  // shared memories, so each SM ingests 32 KB instead of 48 KB per K block.  Measured on B200:
+  // the pair kernel at full width beats both the single-CTA kernels and narrower pair tiles
+  // (shaving the width to even out the last wave costs more in operand re-reads than the
+  // wave saves), so it is used whenever there is more than one 128-row block and more than
+  // 128 columns.  The kernels accept any multiple of 32 as tile width; the router does not
+  // use that freedom yet.
+  if (d->M > 128 && d->N > 128) {
     plan->cluster = 2;
+    best_bn = 256;
     tiles_m = (d->M + 255) / 256;
+    const int64_t tn = (d->N + 255) / 256;
+    const int64_t units = std::max(1, props.sm_count / 2);
+    const int64_t waves = (tiles_m * tn + units - 1) / units;
+    best = std::max(waves * 2.0 * 256.0 * 256.0 * static_cast<double>(k_pad) / (2.0 * per_sm_rate) * 1e6,
+                    plan->t_hbm_us);
   }
+  plan->tile_n = best_bn;
   const int cg = plan->cluster;
   const int64_t tiles_n = (d->N + best_bn - 1) / best_bn;
   const int64_t tiles = tiles_m * tiles_n;
@@ -196,13 +206,15 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
   plan->group_m = static_cast<int32_t>(std::min<int64_t>(cg == 2 ? 4 : 8, tiles_m));
 
   // Shared memory: ring of (A 16 KB + this CTA's share of B) stages under the opt-in budget.
-  const int stage_bytes = 128 * 128 + (best_bn / cg) * 128;
-  const int fixed = 4 * best_bn * 2 * 4 /* column-reduction scratch */ + 256 /* barriers */ + 1024 /* alignment */;
+  const int kernel_bn = best_bn > 128 ? 256 : 128;   // the instance that runs it
+  const int stage_bytes = 128 * 128 + (kernel_bn / cg) * 128;
+  const int fixed = 4 * kernel_bn * 2 * 4 /* column-reduction scratch */ + 4 * kernel_bn * 4 /* staged row vectors */ +
+                    256 /* barriers */ + 1024 /* alignment */;
   int stages = (props.smem_per_block_optin - fixed) / stage_bytes;
-  stages = std::max(2, std::min(stages, cg == 2 ? 6 : (best_bn == 256 ? 4 : 6)));
+  stages = std::max(2, std::min(stages, cg == 2 ? 6 : (kernel_bn == 256 ? 4 : 6)));
   plan->stages = stages;
   plan->smem_bytes = stages * stage_bytes + fixed;
-  plan->tmem_cols = 2 * best_bn;
+  plan->tmem_cols = 2 * kernel_bn;
 
   const double launch_us = 3.0;
   plan->t_est_us = best + launch_us;

@@ -172,26 +172,27 @@ def test_fp32_is_close_to_true_fp32_not_tf32(K):
     assert err < 2.5e-4, err
 
 
-def test_both_tile_widths(K):
-    import ctypes as C
-
+@pytest.mark.parametrize("b_view", ["t", "n"])
+def test_tile_widths_and_cta_pairs(K, b_view):
+    """Every tile width the router may pick (multiples of 32; CTA pairs above 128 columns,
+    a single CTA at 128 and below) gives the same matrix."""
     from fuseml_b200 import _native as N
 
     g = torch.Generator().manual_seed(3)
-    a = torch.randn(384, 256, generator=g).to(torch.bfloat16).cuda()
-    b = (torch.randn(256, 640, generator=g) / 16).to(torch.bfloat16).cuda()
+    a = torch.randn(600, 256, generator=g).to(torch.bfloat16).cuda()
+    b = (torch.randn(256, 1000, generator=g) / 16).to(torch.bfloat16)
+    b = b.cuda() if b_view == "n" else b.t().contiguous().cuda().t()
     ref = (a.float() @ b.float()).cpu().numpy()
-    for tile_n in (128, 256):
-        out = torch.empty(384, 640, dtype=torch.bfloat16, device="cuda")
+    for tile_n, cluster in ((64, 1), (128, 1), (256, 1), (160, 2), (192, 2), (224, 2), (256, 2)):
+        out = torch.full((600, 1000), float("nan"), dtype=torch.bfloat16, device="cuda")
         desc = N.GemmDesc()
         K.fill_desc(desc, a, b, None, out, torch.bfloat16)
         plan = K.plan_for(desc, K.device_props())
-        plan.tile_n = tile_n
-        plan.grid = 5
+        plan.tile_n, plan.cluster, plan.grid = tile_n, cluster, 6
         K.fused_gemm(a, b, None, out=out, plan=plan)
         torch.cuda.synchronize()
         _status_ok(K)
-        np.testing.assert_allclose(out.float().cpu().numpy(), ref, **BF16_TOL)
+        np.testing.assert_allclose(out.float().cpu().numpy(), ref, err_msg=f"tile_n={tile_n} cluster={cluster}", **BF16_TOL)
 
 
 def test_strided_views_without_copies(K):
