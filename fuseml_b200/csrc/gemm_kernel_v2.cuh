@@ -204,25 +204,40 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           // leader's barrier, addressed through the cluster window)
           const uint32_t bar = (CG == 2) ? ptx::mapa(full_bar(stage), 0) : full_bar(stage);
           if (CG == 1 || is_leader) ptx::mbar_arrive_expect_tx(full_bar(stage), CG * stage_tx);
-          // policy: 0 = default, 1 = evict-first (pure stream), 2 = evict-last (keep resident)
-          auto load = [&](uint32_t dst, const CUtensorMap* tm, int32_t c0, int32_t c1, int32_t policy) {
-            if (CG == 2) {
-              if (policy == 1) ptx::tma_load_2d_pair_hint(dst, tm, bar, c0, c1, pol_stream);
-              else if (policy == 2) ptx::tma_load_2d_pair_hint(dst, tm, bar, c0, c1, pol_keep);
-              else ptx::tma_load_2d_pair(dst, tm, bar, c0, c1);
-            } else {
-              if (policy == 1) ptx::tma_load_2d_hint(dst, tm, bar, c0, c1, pol_stream);
-              else if (policy == 2) ptx::tma_load_2d_hint(dst, tm, bar, c0, c1, pol_keep);
-              else ptx::tma_load_2d(dst, tm, bar, c0, c1);
-            }
-          };
-          load(a_dst, &tmap_a, kb * BK, m0, p.a_stream);
-          if (!B_MN) {
-            load(b_dst, &tmap_b, kb * BK, n0, p.b_stream);
-          } else {
+          // L2 policy per operand: 0 = default (plain load), 1 = evict-first (pure stream),
+          // 2 = evict-last (keep resident).  The loads are spelled out per case: routing them
+          // through a helper with run-time policy and box-count tests made the issue of the four
+          // MN-major boxes slow enough to starve the tensor core.
+          const uint64_t pol_a = p.a_stream == 1 ? pol_stream : pol_keep;
+          const uint64_t pol_b = p.b_stream == 1 ? pol_stream : pol_keep;
+          if (CG == 1) {
+            if (p.a_stream == 0) ptx::tma_load_2d(a_dst, &tmap_a, bar, kb * BK, m0);
+            else ptx::tma_load_2d_hint(a_dst, &tmap_a, bar, kb * BK, m0, pol_a);
+            if (!B_MN) {
+              if (p.b_stream == 0) ptx::tma_load_2d(b_dst, &tmap_b, bar, kb * BK, n0);
+              else ptx::tma_load_2d_hint(b_dst, &tmap_b, bar, kb * BK, n0, pol_b);
+            } else if (p.b_stream == 0 && n_boxes == BN_CTA / 64) {
 #pragma unroll
-            for (int j = 0; j < BN_CTA / 64; ++j)
-              if (j < n_boxes) load(b_dst + j * (BK * kSwizzleBytes), &tmap_b, n0 + j * 64, kb * BK, p.b_stream);
+              for (int j = 0; j < BN_CTA / 64; ++j)
+                ptx::tma_load_2d(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK);
+            } else {
+              for (int j = 0; j < n_boxes; ++j)
+                ptx::tma_load_2d_hint(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK, pol_b);
+            }
+          } else {
+            if (p.a_stream == 0) ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, kb * BK, m0);
+            else ptx::tma_load_2d_pair_hint(a_dst, &tmap_a, bar, kb * BK, m0, pol_a);
+            if (!B_MN) {
+              if (p.b_stream == 0) ptx::tma_load_2d_pair(b_dst, &tmap_b, bar, kb * BK, n0);
+              else ptx::tma_load_2d_pair_hint(b_dst, &tmap_b, bar, kb * BK, n0, pol_b);
+            } else if (p.b_stream == 0 && n_boxes == BN_CTA / 64) {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / 64; ++j)
+                ptx::tma_load_2d_pair(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK);
+            } else {
+              for (int j = 0; j < n_boxes; ++j)
+                ptx::tma_load_2d_pair_hint(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK, pol_b);
+            }
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -339,7 +354,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
       // After a failed wait the warp keeps walking its tiles without touching TMEM, so that the
       // named barriers below still see all eight warps.
-      if (ok && !ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kWhereEpilogueTmemFull)) {
+      if (ok && !ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kWhereEpilogueTmemFull, true)) {
         ok = false;
       }
       ptx::tc_fence_after_sync();

@@ -69,11 +69,15 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // `where` in the global status word; everyone else sees the flag at their next
 // poll and returns false as well.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          int32_t* status_word, int32_t where) {
+                                          int32_t* status_word, int32_t where, bool backoff = false) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    // Warps that wait for a whole K loop (the epilogue) must not compete for issue slots with
+    // the single threads that feed TMA and the tensor core on the same scheduler: they sleep
+    // between polls.  The latency-critical waiters (producer, MMA issuer) poll back to back.
+    if (backoff) __nanosleep(it < 64 ? 64 : 256);
     if ((it & 0xFF) == 0) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
