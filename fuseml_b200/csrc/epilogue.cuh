@@ -15,29 +15,100 @@
 namespace fuseml {
 namespace epi {
 
-// 1 + erf(z) without cancellation for negative z: Abramowitz-Stegun 7.1.26 gives
-// erfc(|z|) = poly(t) * exp(-z^2), t = 1/(1 + p|z|), |error| < 1.5e-7; then
-// 1 + erf(z) = erfc(|z|) for z < 0 and 2 - erfc(|z|) otherwise.  Two special-function-unit
-// ops and six FMAs per element, no divergent branch (erff() costs about three times as much).
-__device__ __forceinline__ float one_plus_erf(float z) {
-  const float a = fabsf(z);
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, a, 1.0f));  // MUFU.RCP (an IEEE-rounded reciprocal costs several times more)
-  float poly = fmaf(t, 1.061405429f, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  const float erfc_a = poly * t * __expf(-a * a);
-  return z < 0.0f ? erfc_a : 2.0f - erfc_a;
+// ---- packed fp32 arithmetic (two lanes per instruction, sm_100) ---------------------------
+// Epilogue instructions compete for issue slots with the single threads that feed TMA and the
+// tensor core (measured: every issue cycle of epilogue arithmetic per scheduler costs about one
+// cycle of MMA time), so the element-wise math is written over pairs of columns with the
+// f32x2 forms of add/mul/fma; only the special-function ops and bit operations stay scalar.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
 }
-__device__ __forceinline__ float gelu_erf(float x) {
-  return 0.5f * x * one_plus_erf(x * 0.70710678118654752440f);
+__device__ __forceinline__ void unpack2(f32x2 r, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(r));
 }
-__device__ __forceinline__ float gelu_tanh(float x) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float u = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+__device__ __forceinline__ f32x2 splat2(float c) { return pack2(c, c); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
 }
-__device__ __forceinline__ float sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// GELU (erf form) of two values: 0.5 x (1 + erf(x / sqrt 2)).
+// erf through Abramowitz-Stegun 7.1.26: erfc(|z|) = poly(t) exp(-z^2), t = 1/(1 + p|z|),
+// |error| < 1.5e-7, and erf(z) = copysign(1 - erfc(|z|), z) (no cancellation for either sign).
+// With z = x / sqrt 2 folded into the constants: t = 1/(1 + (p/sqrt 2)|x|),
+// exp(-z^2) = 2^(-(log2 e / 2) x^2).  Two special-function ops per element; the rest is ten
+// packed instructions per pair.
+__device__ __forceinline__ void gelu_erf2(float& x0, float& x1) {
+  const f32x2 x = pack2(x0, x1);
+  const f32x2 ax = pack2(fabsf(x0), fabsf(x1));
+  const f32x2 den = fma2(ax, splat2(0.3275911f * 0.70710678118654752440f), splat2(1.0f));
+  float d0, d1;
+  unpack2(den, d0, d1);
+  const f32x2 t = pack2(rcp_approx(d0), rcp_approx(d1));
+  f32x2 poly = fma2(t, splat2(1.061405429f), splat2(-1.453152027f));
+  poly = fma2(poly, t, splat2(1.421413741f));
+  poly = fma2(poly, t, splat2(-0.284496736f));
+  poly = fma2(poly, t, splat2(0.254829592f));
+  poly = mul2(poly, t);
+  float a0, a1;
+  unpack2(mul2(mul2(x, x), splat2(-0.5f * 1.4426950408889634f)), a0, a1);
+  const f32x2 e = pack2(ex2_approx(a0), ex2_approx(a1));
+  float r0, r1;
+  unpack2(fma2(poly, mul2(e, splat2(-1.0f)), splat2(1.0f)), r0, r1);   // 1 - erfc(|z|) = |erf z|
+  const f32x2 erf = pack2(copysignf(r0, x0), copysignf(r1, x1));
+  const f32x2 hx = mul2(x, splat2(0.5f));
+  unpack2(fma2(hx, erf, hx), x0, x1);
+}
+
+// GELU (tanh form): 0.5 x (1 + tanh u), u = k0 (x + k1 x^3).  0.5 (1 + tanh u) = 1 / (1 + e^(-2u)),
+// so gelu = x / (1 + 2^(x (c0 + c1 x^2))) with c0 = -2 k0 log2 e, c1 = c0 k1.
+__device__ __forceinline__ void gelu_tanh2(float& x0, float& x1) {
+  const float c0 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  const f32x2 x = pack2(x0, x1);
+  const f32x2 w = mul2(x, fma2(mul2(x, x), splat2(c0 * 0.044715f), splat2(c0)));
+  float w0, w1;
+  unpack2(w, w0, w1);
+  // 2^w overflows to +inf for very negative x: x / inf = -0, the correct limit
+  const f32x2 den = add2(pack2(ex2_approx(w0), ex2_approx(w1)), splat2(1.0f));
+  float d0, d1;
+  unpack2(den, d0, d1);
+  unpack2(mul2(x, pack2(rcp_approx(d0), rcp_approx(d1))), x0, x1);
+}
+
+// sigmoid: 1 / (1 + 2^(-x log2 e))
+__device__ __forceinline__ void sigmoid2(float& x0, float& x1) {
+  float w0, w1;
+  unpack2(mul2(pack2(x0, x1), splat2(-1.4426950408889634f)), w0, w1);
+  const f32x2 den = add2(pack2(ex2_approx(w0), ex2_approx(w1)), splat2(1.0f));
+  float d0, d1;
+  unpack2(den, d0, d1);
+  x0 = rcp_approx(d0);
+  x1 = rcp_approx(d1);
+}
 
 __device__ __forceinline__ float load_scalar(const void* p, int64_t idx, int32_t dtype) {
   if (dtype == FUSEML_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
@@ -54,11 +125,18 @@ __device__ __forceinline__ float combine(bool mul, float sa, float sb, float a, 
   return mul ? a * b : fmaf(sb, b, sa * a);
 }
 
+// the same over a pair of columns: one packed instruction
+__device__ __forceinline__ void combine2(bool mul, f32x2 sa, f32x2 sb, float& a0, float& a1, float b0, float b1) {
+  const f32x2 a = pack2(a0, a1), b = pack2(b0, b1);
+  unpack2(mul ? mul2(a, b) : fma2(sb, b, mul2(sa, a)), a0, a1);
+}
+
 __device__ __forceinline__ void fold_operand_chunk(float (&v)[kChunkN], int32_t code, const EpiOperand& o, int64_t m,
                                                    int32_t n0, int32_t N) {
   const bool mul = code == FUSEML_OP_MUL_T;
   const float sa = code == FUSEML_OP_RSUB_T ? -1.0f : 1.0f;
   const float sb = code == FUSEML_OP_SUB_T ? -1.0f : 1.0f;
+  const f32x2 sa2 = splat2(sa), sb2 = splat2(sb);
   const int64_t base = m * o.stride_m + static_cast<int64_t>(n0) * o.stride_n;
   const bool full = (n0 + kChunkN <= N);
   if (o.stride_n == 1 && full) {
@@ -68,10 +146,8 @@ __device__ __forceinline__ void fold_operand_chunk(float (&v)[kChunkN], int32_t 
 #pragma unroll
         for (int i = 0; i < kChunkN / 4; ++i) {
           const float4 q = __ldg(reinterpret_cast<const float4*>(p) + i);
-          v[4 * i + 0] = combine(mul, sa, sb, v[4 * i + 0], q.x);
-          v[4 * i + 1] = combine(mul, sa, sb, v[4 * i + 1], q.y);
-          v[4 * i + 2] = combine(mul, sa, sb, v[4 * i + 2], q.z);
-          v[4 * i + 3] = combine(mul, sa, sb, v[4 * i + 3], q.w);
+          combine2(mul, sa2, sb2, v[4 * i + 0], v[4 * i + 1], q.x, q.y);
+          combine2(mul, sa2, sb2, v[4 * i + 2], v[4 * i + 3], q.z, q.w);
         }
         return;
       }
@@ -87,8 +163,7 @@ __device__ __forceinline__ void fold_operand_chunk(float (&v)[kChunkN], int32_t 
             float2 f;
             if (o.dtype == FUSEML_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
             else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-            v[8 * i + 2 * j] = combine(mul, sa, sb, v[8 * i + 2 * j], f.x);
-            v[8 * i + 2 * j + 1] = combine(mul, sa, sb, v[8 * i + 2 * j + 1], f.y);
+            combine2(mul, sa2, sb2, v[8 * i + 2 * j], v[8 * i + 2 * j + 1], f.x, f.y);
           }
         }
         return;
@@ -109,10 +184,10 @@ __device__ __forceinline__ void fold_staged(float (&v)[kChunkN], const float* sr
 #pragma unroll
   for (int i = 0; i < kChunkN / 4; ++i) {
     const float4 q = reinterpret_cast<const float4*>(src)[i];
-    v[4 * i + 0] = kMul ? v[4 * i + 0] * q.x : v[4 * i + 0] + q.x;
-    v[4 * i + 1] = kMul ? v[4 * i + 1] * q.y : v[4 * i + 1] + q.y;
-    v[4 * i + 2] = kMul ? v[4 * i + 2] * q.z : v[4 * i + 2] + q.z;
-    v[4 * i + 3] = kMul ? v[4 * i + 3] * q.w : v[4 * i + 3] + q.w;
+    const f32x2 lo = pack2(v[4 * i + 0], v[4 * i + 1]), hi = pack2(v[4 * i + 2], v[4 * i + 3]);
+    const f32x2 qlo = pack2(q.x, q.y), qhi = pack2(q.z, q.w);
+    unpack2(kMul ? mul2(lo, qlo) : add2(lo, qlo), v[4 * i + 0], v[4 * i + 1]);
+    unpack2(kMul ? mul2(hi, qhi) : add2(hi, qhi), v[4 * i + 2], v[4 * i + 3]);
   }
 }
 
@@ -187,25 +262,25 @@ __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int3
         break;
       case FUSEML_OP_GELU_ERF:
 #pragma unroll
-        for (int i = 0; i < kChunkN; ++i) v[i] = gelu_erf(v[i]);
+        for (int i = 0; i < kChunkN; i += 2) gelu_erf2(v[i], v[i + 1]);
         break;
       case FUSEML_OP_GELU_TANH:
 #pragma unroll
-        for (int i = 0; i < kChunkN; ++i) v[i] = gelu_tanh(v[i]);
+        for (int i = 0; i < kChunkN; i += 2) gelu_tanh2(v[i], v[i + 1]);
         break;
       case FUSEML_OP_SIGMOID:
 #pragma unroll
-        for (int i = 0; i < kChunkN; ++i) v[i] = sigmoid(v[i]);
+        for (int i = 0; i < kChunkN; i += 2) sigmoid2(v[i], v[i + 1]);
         break;
       case FUSEML_OP_ADD_IMM: {
         const float c = p.ops[op].imm;
 #pragma unroll
-        for (int i = 0; i < kChunkN; ++i) v[i] += c;
+        for (int i = 0; i < kChunkN; i += 2) unpack2(add2(pack2(v[i], v[i + 1]), splat2(c)), v[i], v[i + 1]);
       } break;
       case FUSEML_OP_MUL_IMM: {
         const float c = p.ops[op].imm;
 #pragma unroll
-        for (int i = 0; i < kChunkN; ++i) v[i] *= c;
+        for (int i = 0; i < kChunkN; i += 2) unpack2(mul2(pack2(v[i], v[i + 1]), splat2(c)), v[i], v[i + 1]);
       } break;
       case FUSEML_OP_ADD_T:
       case FUSEML_OP_MUL_T:
@@ -240,13 +315,15 @@ __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int3
       case FUSEML_OP_ADD_SAVED:
         if (kUsesSaved) {
 #pragma unroll
-          for (int i = 0; i < kChunkN; ++i) v[i] += s[i];
+          for (int i = 0; i < kChunkN; i += 2)
+            unpack2(add2(pack2(v[i], v[i + 1]), pack2(s[i], s[i + 1])), v[i], v[i + 1]);
         }
         break;
       case FUSEML_OP_MUL_SAVED:
         if (kUsesSaved) {
 #pragma unroll
-          for (int i = 0; i < kChunkN; ++i) v[i] *= s[i];
+          for (int i = 0; i < kChunkN; i += 2)
+            unpack2(mul2(pack2(v[i], v[i + 1]), pack2(s[i], s[i + 1])), v[i], v[i + 1]);
         }
         break;
       default:

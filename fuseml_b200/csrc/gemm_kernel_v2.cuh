@@ -34,6 +34,19 @@ enum : int32_t {
   kWhereProducerDrain = 0x205,
 };
 
+// Optional stall counters (diagnostic builds only, -DFUSEML_STALL_COUNTERS): per CTA
+//   [0] MMA thread: cycles from first to last tile   [1] ... waiting for operands (full barriers)
+//   [2] ... waiting for a free accumulator buffer     [3] epilogue warp 2: waiting for the accumulator
+//   [4] epilogue warp 2: working                       [5] producer: waiting for a free ring stage
+#ifdef FUSEML_STALL_COUNTERS
+__device__ unsigned long long g_stall[1024][8];
+#define FUSEML_STALL_T0() const long long stall_t0 = clock64()
+#define FUSEML_STALL_ADD(var) var += clock64() - stall_t0
+#else
+#define FUSEML_STALL_T0() do {} while (0)
+#define FUSEML_STALL_ADD(var) do {} while (0)
+#endif
+
 template <int BN, int STAGES, int CG>
 struct Smem {
   static constexpr int kABytes = kTileM * kSwizzleBytes;          // this CTA's 128 rows of A
@@ -188,16 +201,19 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       bool ok = true;
       const uint64_t pol_stream = ptx::policy_evict_first();
       const uint64_t pol_keep = ptx::policy_evict_last();
+      long long st_empty = 0;
       for (int32_t t = unit; t < p.num_tiles && ok; t += num_units) {
         int32_t tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
         const int32_t m0 = tm * (kTileM * CG) + static_cast<int32_t>(cta_rank) * kTileM;
         const int32_t n0 = tn * bn + static_cast<int32_t>(cta_rank) * bn_cta;
         for (int32_t kb = 0; kb < num_kb; ++kb) {
+          FUSEML_STALL_T0();
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWhereProducerEmpty)) {
             ok = false;
             break;
           }
+          FUSEML_STALL_ADD(st_empty);
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
           const uint32_t b_dst = a_dst + L::kABytes;
           // one load helper for both modes: completion bytes go to `bar` (for a pair: the
@@ -243,6 +259,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
+#ifdef FUSEML_STALL_COUNTERS
+      g_stall[blockIdx.x][5] = st_empty;
+#else
+      (void)st_empty;
+#endif
       if (!ok && is_leader) {
         // Giving up: let copies already in flight land before the CTA exits (a pair's bytes are all
         // counted on the leader's barriers, and the partner cannot leave before the final cluster
@@ -272,18 +293,28 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      long long st_full = 0, st_tmem = 0;
+#ifdef FUSEML_STALL_COUNTERS
+      const long long st_begin = clock64();
+#endif
       for (int32_t t = unit; t < p.num_tiles && ok; t += num_units) {
-        if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kWhereMmaTmemEmpty)) {
-          ok = false;
-          break;
+        {
+          FUSEML_STALL_T0();
+          if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kWhereMmaTmemEmpty)) {
+            ok = false;
+            break;
+          }
+          FUSEML_STALL_ADD(st_tmem);
         }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int32_t kb = 0; kb < num_kb; ++kb) {
+          FUSEML_STALL_T0();
           if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.status, kWhereMmaFull)) {
             ok = false;
             break;
           }
+          FUSEML_STALL_ADD(st_full);
           ptx::tc_fence_after_sync();
           const uint32_t a_addr = smem_base + stage * L::kStageBytes;
           const uint32_t b_addr = a_addr + L::kABytes;
@@ -311,6 +342,13 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+#ifdef FUSEML_STALL_COUNTERS
+      g_stall[blockIdx.x][0] = clock64() - st_begin;
+      g_stall[blockIdx.x][1] = st_full;
+      g_stall[blockIdx.x][2] = st_tmem;
+#else
+      (void)st_full; (void)st_tmem;
+#endif
     }
     __syncwarp();
   } else {
@@ -327,6 +365,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const bool red_any = red_sum || red_max;
     float all_sum = 0.0f, all_max = -INFINITY;
     bool ok = true;
+    long long st_wait = 0, st_work = 0;
     for (int32_t t = unit; t < p.num_tiles; t += num_units) {
       int32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
@@ -354,9 +393,14 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
       // After a failed wait the warp keeps walking its tiles without touching TMEM, so that the
       // named barriers below still see all eight warps.
-      if (ok && !ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kWhereEpilogueTmemFull, true)) {
-        ok = false;
+      {
+        FUSEML_STALL_T0();
+        if (ok && !ptx::mbar_wait(tmem_full_bar(acc), acc_phase, abort_flag, p.status, kWhereEpilogueTmemFull, true)) {
+          ok = false;
+        }
+        FUSEML_STALL_ADD(st_wait);
       }
+      FUSEML_STALL_T0();
       ptx::tc_fence_after_sync();
       float row_sum = 0.0f, row_max = -INFINITY;
 #pragma unroll 1
@@ -395,6 +439,21 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             }
             if (red_sum) colred[(quarter * 2 + 0) * BN + c * kChunkN + lane] = warp_column_reduce<false>(vs, lane);
             if (red_max) colred[(quarter * 2 + 1) * BN + c * kChunkN + lane] = warp_column_reduce<true>(vm, lane);
+          } else if (n0 + kChunkN <= p.N) {
+            // full chunk: pairwise packed adds (two chains), maxima as a tree
+            epi::f32x2 s0 = epi::pack2(v[0], v[1]), s1 = epi::pack2(v[2], v[3]);
+            float m0 = fmaxf(v[0], v[1]), m1 = fmaxf(v[2], v[3]);
+#pragma unroll
+            for (int i = 4; i < kChunkN; i += 4) {
+              s0 = epi::add2(s0, epi::pack2(v[i], v[i + 1]));
+              s1 = epi::add2(s1, epi::pack2(v[i + 2], v[i + 3]));
+              m0 = fmaxf(m0, fmaxf(v[i], v[i + 1]));
+              m1 = fmaxf(m1, fmaxf(v[i + 2], v[i + 3]));
+            }
+            float lo, hi;
+            epi::unpack2(epi::add2(s0, s1), lo, hi);
+            row_sum += lo + hi;
+            row_max = fmaxf(row_max, fmaxf(m0, m1));
           } else {
 #pragma unroll
             for (int i = 0; i < kChunkN; ++i) {
@@ -412,6 +471,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (CG == 2) ptx::mbar_arrive_cluster(lead_tmem_empty0 + 8u * acc);
         else ptx::mbar_arrive(tmem_empty_bar(acc));
       }
+      FUSEML_STALL_ADD(st_work);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
 
@@ -446,6 +506,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         }
       }
     }
+#ifdef FUSEML_STALL_COUNTERS
+    if (warp == 2 && lane == 0) { g_stall[blockIdx.x][3] = st_wait; g_stall[blockIdx.x][4] = st_work; }
+#else
+    (void)st_wait; (void)st_work;
+#endif
     if (red_any && p.red_axis == FUSEML_AXIS_ALL) {
       const float ws = warp_sum(all_sum);
       const float wm = warp_max(all_max);

@@ -12,8 +12,6 @@ namespace fuseml {
 
 constexpr int kTileM = 128;        // UMMA M with cta_group::1: one TMEM lane per row
 constexpr int kSwizzleBytes = 128; // K extent of one shared-memory stage, in bytes
-constexpr int kNumThreads = 192;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
-constexpr int kEpilogueWarps = 4;
 constexpr int kChunkN = 32;        // accumulator columns one tcgen05.ld brings in
 
 struct EpiOperand {
