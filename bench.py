@@ -570,7 +570,7 @@ def main():
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_kind": f"hbm_gbs, {peak_src}"}
     roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
-    roof["kernel"] = "gemm_epilogue_kernel"
+    roof["kernel"] = "gemm_epilogue_kernel_v2"
     roof["launch_us"] = launch_ms * 1e3
 
     line = {

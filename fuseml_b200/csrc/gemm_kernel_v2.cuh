@@ -294,6 +294,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       uint32_t acc_phase = 0;
       bool ok = true;
       long long st_full = 0, st_tmem = 0;
+      bool ready = false;   // the next ring stage is already known to be full
 #ifdef FUSEML_STALL_COUNTERS
       const long long st_begin = clock64();
 #endif
@@ -309,13 +310,20 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int32_t kb = 0; kb < num_kb; ++kb) {
-          FUSEML_STALL_T0();
-          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.status, kWhereMmaFull)) {
-            ok = false;
-            break;
+          // `ready` carries the result of a probe issued just before the previous K block's MMAs:
+          // the barrier's round trip overlaps their issue instead of preceding the next ones
+          if (!ready) {
+            FUSEML_STALL_T0();
+            if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, p.status, kWhereMmaFull)) {
+              ok = false;
+              break;
+            }
+            FUSEML_STALL_ADD(st_full);
           }
-          FUSEML_STALL_ADD(st_full);
           ptx::tc_fence_after_sync();
+          const int next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
+          const uint32_t next_phase = (stage + 1 == STAGES) ? (phase ^ 1u) : phase;
+          const bool next_ready = ptx::mbar_try_wait(full_bar(next_stage), next_phase);
           const uint32_t a_addr = smem_base + stage * L::kStageBytes;
           const uint32_t b_addr = a_addr + L::kABytes;
           const uint64_t a_desc = ptx::make_smem_desc_sw128(a_addr, 16u, 1024u);
@@ -335,7 +343,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             }
           }
           if (CG == 2) ptx::mma_commit_pair(empty_bar(stage)); else ptx::mma_commit(empty_bar(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          stage = next_stage;
+          phase = next_phase;
+          ready = next_ready;
         }
         if (!ok) break;
         if (CG == 2) ptx::mma_commit_pair(tmem_full_bar(acc)); else ptx::mma_commit(tmem_full_bar(acc));
