@@ -92,16 +92,23 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const G
     configured_device = dev;
   }
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the
+  // stream drains; it waits (griddepcontrol.wait) before its first global access.
+  attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+  ++n_attr;
   if (CG == 2) {
     int pairs = grid / 2;
     if (max_clusters > 0 && pairs > max_clusters) pairs = max_clusters;
     if (pairs < 1) pairs = 1;
     grid = 2 * pairs;
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2; attr[n_attr].val.clusterDim.y = 1; attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
   }
+  cfg.attrs = attr; cfg.numAttrs = n_attr;
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(v2::kThreads);
   cfg.dynamicSmemBytes = L::kDynamicBytes;
@@ -501,7 +508,7 @@ int fuseml_sm100_device_status(void* cuda_stream, int32_t* status_out) {
 // diagnostic builds only: copy the per-CTA stall counters of the last launches to the host
 int fuseml_debug_stalls(unsigned long long* out, int ctas) {
   if (ctas > 1024) ctas = 1024;
-  return cudaMemcpyFromSymbol(out, fuseml::v2::g_stall, sizeof(unsigned long long) * 8 * ctas) == cudaSuccess ? 0 : 1;
+  return cudaMemcpyFromSymbol(out, fuseml::v2::g_stall, sizeof(unsigned long long) * 12 * ctas) == cudaSuccess ? 0 : 1;
 }
 #endif
 

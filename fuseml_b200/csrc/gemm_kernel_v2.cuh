@@ -38,8 +38,11 @@ enum : int32_t {
 //   [0] MMA thread: cycles from first to last tile   [1] ... waiting for operands (full barriers)
 //   [2] ... waiting for a free accumulator buffer     [3] epilogue warp 2: waiting for the accumulator
 //   [4] epilogue warp 2: working                       [5] producer: waiting for a free ring stage
+//   [6] wall clock (ns) at kernel entry                [7] wall clock (ns) just before the CTA exits
+//   [8] ... after set-up (barriers, TMEM, cluster sync) [9] ... when the MMA thread has issued everything
+//   [10] ... when epilogue warp 2 is done               [11] ... after the tear-down barriers
 #ifdef FUSEML_STALL_COUNTERS
-__device__ unsigned long long g_stall[1024][8];
+__device__ unsigned long long g_stall[1024][12];
 #define FUSEML_STALL_T0() const long long stall_t0 = clock64()
 #define FUSEML_STALL_ADD(var) var += clock64() - stall_t0
 #else
@@ -147,6 +150,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef FUSEML_STALL_COUNTERS
+  if (threadIdx.x == 0) g_stall[blockIdx.x][6] = ptx::globaltimer_ns();
+#endif
   const uint32_t cta_rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;
   const bool is_leader = (cta_rank == 0);
   const int32_t unit = blockIdx.x / CG;            // tile walker id (CTA or pair)
@@ -184,7 +190,15 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     ptx::cluster_wait();
   }
   ptx::tc_fence_after_sync();
+  // Everything above touched only this CTA's shared memory, TMEM and the kernel parameters; it
+  // may overlap the tail of the previous kernel of the stream.  From here on global memory is
+  // read and written: wait for the previous kernel first.
+  ptx::griddep_launch_dependents();
+  ptx::griddep_wait();
   const uint32_t tmem_base = *tmem_base_slot;
+#ifdef FUSEML_STALL_COUNTERS
+  if (threadIdx.x == 32) g_stall[blockIdx.x][8] = ptx::globaltimer_ns();
+#endif
   const int32_t num_kb = p.num_kb;
   // The tile width is a run-time value (a multiple of 32, at most BN): the router may shave it
   // so that the number of tiles fits the number of CTA pairs without a ragged last wave.
@@ -354,6 +368,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
 #ifdef FUSEML_STALL_COUNTERS
       g_stall[blockIdx.x][0] = clock64() - st_begin;
+      g_stall[blockIdx.x][9] = ptx::globaltimer_ns();
       g_stall[blockIdx.x][1] = st_full;
       g_stall[blockIdx.x][2] = st_tmem;
 #else
@@ -517,7 +532,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
     }
 #ifdef FUSEML_STALL_COUNTERS
-    if (warp == 2 && lane == 0) { g_stall[blockIdx.x][3] = st_wait; g_stall[blockIdx.x][4] = st_work; }
+    if (warp == 2 && lane == 0) {
+      g_stall[blockIdx.x][3] = st_wait;
+      g_stall[blockIdx.x][4] = st_work;
+      g_stall[blockIdx.x][10] = ptx::globaltimer_ns();
+    }
 #else
     (void)st_wait; (void)st_work;
 #endif
@@ -545,10 +564,16 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     ptx::cluster_arrive();
     ptx::cluster_wait();
   }
+#ifdef FUSEML_STALL_COUNTERS
+  if (threadIdx.x == 32) g_stall[blockIdx.x][11] = ptx::globaltimer_ns();
+#endif
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     if (CG == 2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols); else ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
+#ifdef FUSEML_STALL_COUNTERS
+  if (threadIdx.x == 32) g_stall[blockIdx.x][7] = ptx::globaltimer_ns();
+#endif
 }
 
 }  // namespace v2

@@ -89,6 +89,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may be scheduled while
+// the previous kernel of the stream is still running.  griddep_wait() blocks until that kernel
+// (and everything before it) has completed and its writes are visible: every thread calls it
+// before touching global memory.  griddep_launch_dependents() tells the scheduler that the next
+// kernel of the stream may be launched as soon as SMs free up.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA ----------------------------------------------------------------------
 
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm) {
