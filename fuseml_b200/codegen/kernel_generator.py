@@ -20,7 +20,7 @@ import torch
 
 from .. import _native as N
 from .._logging import logger
-from ..passes.topology import GLOBAL_REDUCTION_OPS, REDUCTION_OPS, TRANSPARENT_OPS
+from ..passes.topology import GLOBAL_REDUCTION_OPS, REDUCTION_OPS, TRANSPARENT_OPS, reduction_axis_code
 
 _aten = torch.ops.aten
 
@@ -293,12 +293,18 @@ class Sm100KernelGenerator:
             return ReductionInfo(axis=2, op=kind)
         args = _args_of(group, node)
         dims = args[1] if len(args) > 1 else []
-        if isinstance(dims, int):
-            dims = [dims]
-        dims = tuple(sorted({int(d) % 2 for d in dims})) if dims else (0, 1)
-        axis = {(1,): 1, (0,): 0, (0, 1): 2}.get(dims)
+        # rows are the flattened leading dimensions of the reduced tensor ([B, S, N] -> [B*S, N])
+        src = args[0] if args else None
+        shape = None
+        for key in ("tensor_meta", "val"):
+            m = getattr(src, "meta", {}).get(key) if src is not None else None
+            if m is not None and hasattr(m, "shape"):
+                shape = m.shape
+                break
+        rank = len(shape) if shape is not None else 2
+        axis = {"n": 1, "m": 0, "all": 2}.get(reduction_axis_code(dims, rank))
         if axis is None:
-            raise UnsupportedChainError(f"{node.name}: reduction dims {dims}")
+            raise UnsupportedChainError(f"{node.name}: reduction dims {dims} of a rank-{rank} tensor")
         keepdim = bool(args[2]) if len(args) > 2 else False
         if keepdim:
             raise UnsupportedChainError(f"{node.name}: keepdim=True reductions are not fused")

@@ -25,6 +25,7 @@ import torch
 from .. import _native as N
 from .. import kernels as K
 from .._logging import logger
+from ..passes.topology import classify_epilogue_operand
 from .kernel_generator import KernelSpec, TensorDescriptor
 
 _DEFAULT_BLOCK_SIZE_M = 128
@@ -51,6 +52,13 @@ class LaunchParams:
     num_stages: int
 
 
+def _prod(shape) -> int:
+    n = 1
+    for v in shape:
+        n *= int(v)
+    return n
+
+
 def compute_launch_params(M: int, Ncols: int, Kd: int, dtype: torch.dtype = torch.bfloat16, *,
                           block_size_m: int = _DEFAULT_BLOCK_SIZE_M, block_size_n: int = _DEFAULT_BLOCK_SIZE_N,
                           block_size_k: int = _DEFAULT_BLOCK_SIZE_K, group_size_m: int = _DEFAULT_GROUP_SIZE_M,
@@ -73,7 +81,8 @@ def compute_launch_params(M: int, Ncols: int, Kd: int, dtype: torch.dtype = torc
 
 class _Prepared:
     """One (shape, stride) signature: filled descriptor, plan, workspace size, output shapes."""
-    __slots__ = ("desc", "plan", "ws_bytes", "ws", "M", "N", "K", "red_len", "left", "right")
+    __slots__ = ("desc", "plan", "ws_bytes", "ws", "M", "N", "K", "red_len", "left", "right",
+                 "views", "out_shape", "aux_shapes", "red_shape")
 
 
 class KernelLauncher:
@@ -87,7 +96,8 @@ class KernelLauncher:
                  block_size_k: int = _DEFAULT_BLOCK_SIZE_K, group_size_m: int = _DEFAULT_GROUP_SIZE_M,
                  reduction_op: str | None = None, reduction_axis: int | None = None,
                  eager_fn: Callable | None = None, is_autotuned: bool = False, sram_autotuner: Any = None,
-                 mean_epilogue_fused: bool = True, reduction_dtypes: Sequence[torch.dtype] | None = None) -> None:
+                 mean_epilogue_fused: bool = True, reduction_dtypes: Sequence[torch.dtype] | None = None,
+                 reduction_shape: Sequence[int] | None = None) -> None:
         self.__name__ = "fuseml_fused_kernel"
         if not isinstance(kernel_fn, KernelSpec):
             raise TypeError("kernel_fn must be a KernelSpec (the lowered form of a FusionGroup)")
@@ -115,6 +125,9 @@ class KernelLauncher:
         self._is_reduced = bool(self._reductions) and not kernel_fn.store_output and not intermediate_descriptors
         self._reduction_dtypes = list(reduction_dtypes) if reduction_dtypes is not None else \
             [output_descriptor.dtype] * len(self._reductions)
+        # shape the graph expects of a per-row reduction when the rows are grouped ([B, S])
+        self._row_reduction_shape = tuple(int(v) for v in reduction_shape) \
+            if reduction_shape is not None and len(reduction_shape) != 1 else None
         self._launch_params = launch_params
         self._is_autotuned = is_autotuned
         self._sram_autotuner = sram_autotuner
@@ -146,8 +159,57 @@ class KernelLauncher:
     def _materialize_if_needed(t: torch.Tensor) -> torch.Tensor:
         return t.contiguous() if any(s < 0 for s in t.stride()) else t
 
+    def _operand_views(self, inputs: Sequence[torch.Tensor]) -> list:
+        """Per input: the 2-D (or 0-D) shape the kernel addresses it by, or None when it is used
+        as it is.  A with leading batch dimensions is flattened to ``[M, K]``; epilogue operands
+        are lined up with the flattened ``[M, N]`` tile (full, one per row, one per column, scalar)."""
+        views: list = [None] * len(inputs)
+        left, right = inputs[self._left_idx], inputs[self._right_idx]
+        if left.dim() > 2:
+            views[self._left_idx] = (-1, left.shape[-1])
+        if left.dim() < 2 or right.dim() != 2:
+            return views
+        rows = left.numel() // max(1, left.shape[-1])
+        n_cols = right.shape[1]
+        for idx in self._slot_inputs:
+            t = inputs[idx]
+            if idx in (self._left_idx, self._right_idx) or t.dim() <= 2:
+                continue          # 0-D, 1-D and 2-D operands are addressed by their own strides
+            kind = classify_epilogue_operand(t.shape, rows, n_cols)
+            if kind is None:
+                raise N.NativeLibraryError(
+                    f"operand of shape {tuple(t.shape)} does not broadcast to {rows} rows x {n_cols} columns "
+                    f"(A {tuple(left.shape)}, B {tuple(right.shape)}, inputs {[tuple(i.shape) for i in inputs]})")
+            views[idx] = {"full": (rows, n_cols), "row": (1, n_cols), "col": (rows, 1), "scalar": ()}[kind]
+        return views
+
+    @staticmethod
+    def _apply_views(inputs: Sequence[torch.Tensor], views: Sequence) -> tuple:
+        return tuple(t if v is None else t.reshape(v) for t, v in zip(inputs, views))
+
+    def _output_shapes(self, M: int, Ncols: int):
+        """Shapes the graph expects where they differ from the kernel's ``[M, N]`` / ``[M]``:
+        (primary, [per escape store], row reductions)."""
+        def grouped(desc, numel, last):
+            shp = tuple(getattr(desc, "shape", ()) or ())
+            n = 1
+            for v in shp:
+                n *= v
+            if len(shp) in (0, 2 if last else 1) or n != numel or (last and shp[-1] != Ncols):
+                return None
+            return shp
+        out_shape = grouped(self._output_descriptor, M * Ncols, True) if self._spec.store_output else None
+        aux = [grouped(self._intermediate_descriptors[i], M * Ncols, True) for i in self._aux_slots]
+        red_shape = None
+        if self._reductions and self._reductions[0].axis == 1:
+            if self._row_reduction_shape is not None and _prod(self._row_reduction_shape) == M:
+                red_shape = self._row_reduction_shape
+        return out_shape, (aux if any(a is not None for a in aux) else None), red_shape
+
     def _prepare(self, inputs: Sequence[torch.Tensor], key: tuple) -> _Prepared:
         spec = self._spec
+        views = self._operand_views(inputs)
+        inputs = self._apply_views(inputs, views)
         left, right = inputs[self._left_idx], inputs[self._right_idx]
         if left.dim() != 2 or right.dim() != 2:
             raise N.NativeLibraryError("fused GEMM operands must be 2-D")
@@ -196,6 +258,8 @@ class KernelLauncher:
         if p.ws_bytes < 0:
             raise N.NativeLibraryError("fuseml_sm100_workspace_bytes rejected the descriptor")
         p.ws = {}
+        p.views = views if any(v is not None for v in views) else None
+        p.out_shape, p.aux_shapes, p.red_shape = self._output_shapes(M, Ncols)
         self._prepared[key] = p
         logger.debug("prepared launch M=%d N=%d K=%d tile_n=%d grid=%d ws=%d B", M, Ncols, Kd,
                      p.plan.tile_n, p.plan.grid, p.ws_bytes)
@@ -215,6 +279,8 @@ class KernelLauncher:
             p = self._prepare(input_tensors, key)
         spec = self._spec
         desc = p.desc
+        if p.views is not None:
+            input_tensors = self._apply_views(input_tensors, p.views)
         left, right = input_tensors[self._left_idx], input_tensors[self._right_idx]
         if left.stride(1) != 1 and p.K != 1:
             left = left.contiguous()
@@ -259,6 +325,13 @@ class KernelLauncher:
         self.launch_count += 1
         # reductions come back in fp32; hand them over in the dtype the graph expects
         red_out = [t if t.dtype == dt else t.to(dt) for t, dt in zip(red_out, self._reduction_dtypes)]
+        # the kernel works on [M, N]; the graph may see the rows grouped ([B, S, N], [B, S])
+        if p.out_shape is not None and primary is not None:
+            primary = primary.view(p.out_shape)
+        if p.aux_shapes is not None:
+            aux_out = [t if shp is None else t.view(shp) for t, shp in zip(aux_out, p.aux_shapes)]
+        if p.red_shape is not None:
+            red_out = [t.view(p.red_shape) for t in red_out]
         if primary is not None:
             outputs.append(primary)
         outputs.extend(aux_out)

@@ -36,7 +36,7 @@ from .fusion_group import FusionGroup
 from .passes.control_flow_validation import ControlFlowError, validate_graph_control_flow
 from .passes.fusion_pass import FuseMLFusionPass, fuseml_fused_kernel_placeholder
 from .passes.graph_cut import split_fusion_group
-from .passes.topology import is_trigger
+from .passes.topology import classify_epilogue_operand, is_trigger
 from .registry import SupportedOpsRegistry, build_default_registry
 
 _SUPPORTED_DTYPES = (torch.bfloat16, torch.float16, torch.float32)
@@ -185,12 +185,20 @@ class FuseMLCompiler:
         if any(d is None for d in descs):
             raise UnsupportedChainError("missing shape metadata on a group input")
         left, right = descs[spec.left_index], descs[spec.right_index]
-        if len(left.shape) != 2 or len(right.shape) != 2:
-            raise UnsupportedChainError("GEMM operands are not 2-D")
+        if len(left.shape) < 2 or len(right.shape) != 2:
+            raise UnsupportedChainError("GEMM operands: A needs at least two dimensions, B exactly two")
         if left.dtype != right.dtype or left.dtype not in _SUPPORTED_DTYPES:
             raise UnsupportedChainError(f"operand dtypes {left.dtype} / {right.dtype}")
         if 0 in left.shape or 0 in right.shape:
             raise UnsupportedChainError("empty GEMM operand")
+        if len(left.shape) > 2:
+            # [B, S, K] activations: the launcher flattens the leading dimensions (a view when
+            # they collapse, a contiguous copy otherwise), so A is checked as row-major [M, K]
+            rows = 1
+            for v in left.shape[:-1]:
+                rows *= v
+            kdim = left.shape[-1]
+            left = TensorDescriptor(left.name, (rows, kdim), (kdim, 1), left.dtype)
         if left.dtype != torch.float32:
             for d, role in ((left, "A"), (right, "B")):
                 fp = TensorFingerprint(d.shape, d.stride, 0, True, str(d.dtype), tuple(s == 0 for s in d.stride))
@@ -202,13 +210,11 @@ class FuseMLCompiler:
         for st in spec.steps:
             if st.input_index >= 0:
                 d = descs[st.input_index]
-                if d.dtype not in _SUPPORTED_DTYPES or len(d.shape) > 2:
-                    raise UnsupportedChainError(f"epilogue operand {d.name}: dtype {d.dtype}, rank {len(d.shape)}")
-                shp = d.shape
-                ok = (len(shp) == 0 or (len(shp) == 1 and shp[0] in (1, Ncols, M)) or
-                      (len(shp) == 2 and shp[0] in (1, M) and shp[1] in (1, Ncols)))
-                if not ok:
-                    raise UnsupportedChainError(f"epilogue operand {d.name} of shape {shp} does not broadcast to [{M},{Ncols}]")
+                if d.dtype not in _SUPPORTED_DTYPES:
+                    raise UnsupportedChainError(f"epilogue operand {d.name}: dtype {d.dtype}")
+                if classify_epilogue_operand(d.shape, M, Ncols) is None:
+                    raise UnsupportedChainError(f"epilogue operand {d.name} of shape {d.shape} does not broadcast to "
+                                                f"{M} rows x {Ncols} columns")
         out = group.output_metadata
         if spec.store_output and out.get("dtype") not in _SUPPORTED_DTYPES:
             src = group.output_node if not group.extra_outputs else group.output_node
@@ -228,9 +234,12 @@ class FuseMLCompiler:
         inter = [_node_to_descriptor(n) for n in group.intermediate_outputs]
         red_nodes = [n for n in group.all_nodes if n.op == "call_function" and n.target in _RED_KIND]
         red_dtypes = []
+        red_shape = None
         for n in red_nodes[:len(spec.reductions)]:
             d = _node_to_descriptor(n)
             red_dtypes.append(d.dtype if d is not None else torch.float32)
+            if d is not None and red_shape is None:
+                red_shape = d.shape
         if len(red_dtypes) != len(spec.reductions):
             red_dtypes = [torch.float32] * len(spec.reductions)
 
@@ -242,7 +251,7 @@ class FuseMLCompiler:
                 return hit
         launcher = KernelLauncher(
             spec, descs, out_desc, inter, descs[spec.left_index].name, descs[spec.right_index].name,
-            is_autotuned=True, reduction_dtypes=red_dtypes)
+            is_autotuned=True, reduction_dtypes=red_dtypes, reduction_shape=red_shape)
         if key is not None:
             self._cache.store(key, launcher)
         self.launchers.append(launcher)

@@ -35,8 +35,8 @@ from .graph_cut import split_fusion_group, validate_fusion_group  # noqa: F401  
 from .mutation_safety import is_safe_inplace
 from .topology import (ABSORBABLE_OPS, BARRIER_OPS, GLOBAL_REDUCTION_OPS, INPLACE_OPS, REDUCTION_OPS,  # noqa: F401
                        TRANSPARENT_OPS, TRIGGER_OPS, NodeRole, classify_node, gemm_roofline,
-                       is_compute_bound_gemm, is_trigger, resolve_to_defining_node, symint_safe_eq,
-                       symint_safe_len)
+                       RESHAPE_OPS, is_compute_bound_gemm, is_trigger, reduction_axis_code,
+                       resolve_through_reshapes, resolve_to_defining_node, symint_safe_eq, symint_safe_len)
 
 _aten = torch.ops.aten
 
@@ -76,14 +76,14 @@ def _trigger_mnk(node: torch.fx.Node):
 
 
 def _reduction_axis(node: torch.fx.Node):
-    """'n' (per row), 'm' (per column), 'all', or None if the dims are not a 2-D reduction we run."""
+    """'n' (per row), 'm' (per column), 'all', or None if the dims are not a reduction the kernel
+    runs.  Rows are the flattened leading dimensions of the reduced tensor."""
     if node.target in GLOBAL_REDUCTION_OPS:
         return "all"
+    shape = _node_shape(node.args[0]) if node.args else None
+    rank = len(shape) if shape is not None else 2
     dims = node.args[1] if len(node.args) > 1 else []
-    if isinstance(dims, int):
-        dims = [dims]
-    dims = sorted({d % 2 for d in dims}) if dims else [0, 1]
-    return {(1,): "n", (0,): "m", (0, 1): "all"}.get(tuple(dims))
+    return reduction_axis_code(dims, rank)
 
 
 def _reduction_keepdim(node: torch.fx.Node) -> bool:
@@ -165,11 +165,11 @@ class FuseMLFusionPass:
             if role in (NodeRole.UNKNOWN, NodeRole.BARRIER):
                 break
             if role is NodeRole.REDUCTION:
-                if not _reduction_keepdim(nxt):
+                if not _reduction_keepdim(nxt) and _reduction_axis(nxt) is not None:
                     take(nxt)
                 break
             if role is NodeRole.TRANSPARENT:
-                if not self._is_shape_preserving_2d(nxt):
+                if not (self._is_shape_preserving_2d(nxt) or self._is_row_preserving_view(nxt)):
                     break
                 take(nxt, is_output=False)   # a view is never the "real" output
                 cur = nxt
@@ -186,6 +186,14 @@ class FuseMLFusionPass:
                 cur = nxt
                 continue
             break
+
+        # views after the last real op stay in the graph as views of the fused output: absorbing
+        # them would make the kernel store the same values twice (once per name)
+        while group.fused_nodes and group.fused_nodes[-1] is not group.output_node \
+                and classify_node(group.fused_nodes[-1]) is NodeRole.TRANSPARENT:
+            tail = group.fused_nodes.pop()
+            members.discard(tail)
+            claimed.discard(tail)
 
         # escape nodes: interior values somebody outside still reads
         extra = set(group.extra_outputs)
@@ -320,11 +328,14 @@ class FuseMLFusionPass:
     @staticmethod
     def _collect_external_inputs(node: torch.fx.Node, group_node_set: set, group: FusionGroup) -> None:
         """Append ``node``'s outside producers to ``group.inputs`` (order of first use), looking
-        through view ops to the node that really defines the data."""
+        through pure reshapes to the tensor they regroup (``view(x, [B*S, D])`` -> ``x``: the
+        launcher flattens it again).  The reference walks back through every view op
+        (fuseml/passes/fusion_pass.py:321-331 there); behind a permute, slice or expand the
+        defining tensor holds other elements per position, so here those views stay the input."""
         for arg in node.args:
             if not isinstance(arg, torch.fx.Node) or arg in group_node_set:
                 continue
-            resolved = resolve_to_defining_node(arg)
+            resolved = resolve_through_reshapes(arg)
             src = resolved if resolved not in group_node_set else arg
             if src not in group.inputs:
                 group.inputs.append(src)
@@ -342,6 +353,21 @@ class FuseMLFusionPass:
         if symint_safe_len(meta.shape) != 2 or symint_safe_len(pmeta.shape) != 2:
             return False
         return symint_safe_eq(meta.shape[0], pmeta.shape[0]) and symint_safe_eq(meta.shape[1], pmeta.shape[1])
+
+    @staticmethod
+    def _is_row_preserving_view(node: torch.fx.Node) -> bool:
+        """A reshape that only regroups the leading dimensions, ``[M, N] <-> [B, S, N]``: the chain
+        value keeps its rows and columns, so the kernel (which works on the flattened ``[M, N]``)
+        does not see it.  This is what ``nn.Linear`` puts around ``addmm`` for 3-D activations; the
+        reference stops the chain there (fuseml/passes/fusion_pass.py:244-257, 537-579)."""
+        if node.target not in RESHAPE_OPS or not node.args or not isinstance(node.args[0], torch.fx.Node):
+            return False
+        shape, pshape = _node_shape(node), _node_shape(node.args[0])
+        if shape is None or pshape is None:
+            return False
+        if (symint_safe_len(shape) or 0) < 2 or (symint_safe_len(pshape) or 0) < 2:
+            return False
+        return symint_safe_eq(shape[-1], pshape[-1])
 
     @staticmethod
     def _fetch_attr(gm: torch.fx.GraphModule, target: str):

@@ -109,6 +109,82 @@ def resolve_to_defining_node(node: torch.fx.Node) -> torch.fx.Node:
     return cur
 
 
+# Views that only regroup dimensions: element order in memory is what it was.
+RESHAPE_OPS: set[Callable] = {_aten.view.default, _aten._unsafe_view.default, _aten.reshape.default}
+
+
+def resolve_through_reshapes(node: torch.fx.Node) -> torch.fx.Node:
+    """Like :func:`resolve_to_defining_node`, but only through pure reshapes.  A group input
+    found this way can be handed to the kernel in place of the view: flattening it again gives
+    the same elements in the same order.  (Behind a permute, slice, select or expand the
+    defining tensor holds *different* elements per position, so those views stay the input.)"""
+    seen: set = set()
+    cur = node
+    while cur.op == "call_function" and cur.target in RESHAPE_OPS and cur not in seen:
+        seen.add(cur)
+        if not cur.args or not isinstance(cur.args[0], torch.fx.Node):
+            break
+        cur = cur.args[0]
+    return cur
+
+
+def reduction_axis_code(dims: Any, rank: int) -> str | None:
+    """Which kernel reduction a ``dim`` argument means for an input of ``rank`` dimensions whose
+    leading dimensions are the flattened rows: 'n' (over the last dimension: one result per
+    row), 'm' (2-D only: one result per column), 'all', or None (not a reduction the kernel runs,
+    e.g. over the sequence dimension of a [B, S, N] tensor)."""
+    if rank < 1:
+        return None
+    if dims is None or dims == [] or dims == ():
+        return "all"
+    if isinstance(dims, int):
+        dims = [dims]
+    try:
+        norm = tuple(sorted({int(d) % rank for d in dims}))
+    except (TypeError, ValueError):
+        return None
+    if norm == tuple(range(rank)):
+        return "all"
+    if norm == (rank - 1,):
+        return "n"
+    if rank == 2 and norm == (0,):
+        return "m"
+    return None
+
+
+def classify_epilogue_operand(shape: Any, rows: int, n_cols: int) -> str | None:
+    """How an outside operand of ``shape`` lines up with chain values of ``rows`` flattened rows
+    and ``n_cols`` columns (visible shape ``[..., n_cols]``, any grouping of the rows):
+    'scalar', 'row' (one value per column), 'col' (one value per row), 'full', or None when it
+    broadcasts some other way (e.g. ``[S, N]`` against ``[B, S, N]``)."""
+    try:
+        s = tuple(int(v) for v in shape)
+        rows, n_cols = int(rows), int(n_cols)
+    except (TypeError, ValueError):
+        return None
+    one_d = len(s) == 1
+    numel = 1
+    for v in s:
+        numel *= v
+    if numel == 1:
+        return "scalar"
+    while len(s) > 1 and s[0] == 1:
+        s = s[1:]
+    if s == (n_cols,):
+        return "row"
+    if one_d:
+        # the reference's 1-D rule: length N runs along N, else length M along M
+        return "col" if s == (rows,) else None
+    lead = 1
+    for v in s[:-1]:
+        lead *= v
+    if lead == rows and s[-1] == n_cols:
+        return "full"
+    if lead == rows and s[-1] == 1:
+        return "col"
+    return None
+
+
 # ---- SymInt-safe helpers ------------------------------------------------------------
 
 def symint_safe_eq(a: Any, b: Any) -> bool:

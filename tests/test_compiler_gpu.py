@@ -126,3 +126,49 @@ def test_host_streamed_runtime_matches_direct_call(native_lib):
     with pytest.raises(ValueError):
         runner.submit(torch.zeros(4, d, dtype=torch.bfloat16), y_host)     # not pinned
     torch._dynamo.reset()
+
+
+def test_batched_activations_run_fused_and_match_the_flattened_block(native_lib):
+    """The residual MLP block on [B, S, D] activations (what an unmodified Transformer layer
+    feeds it): two fused kernels, 3-D outputs, same numbers as the block on the flattened
+    [B*S, D] input (which the 2-D parity tests pin against the reference) and within the bf16
+    tolerance of the fp32 oracle chain; the row maximum comes back as [B, S]."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+    from oracle import chain
+
+    class Block(torch.nn.Module):
+        def __init__(self, d, i):
+            super().__init__()
+            self.fc1 = torch.nn.Linear(d, i)
+            self.fc2 = torch.nn.Linear(i, d)
+
+        def forward(self, x):
+            y = self.fc2(torch.nn.functional.gelu(self.fc1(x))) + x
+            return y, y.amax(-1)
+
+    torch._dynamo.reset()
+    torch.manual_seed(0)
+    B, S, D, I = 3, 200, 256, 512           # 600 rows: ragged against the 128/256-row tiles
+    block = Block(D, I).to(device="cuda", dtype=torch.bfloat16).eval()
+    x = torch.randn(B, S, D, device="cuda", dtype=torch.bfloat16)
+    comp = F.FuseMLCompiler()
+    compiled = torch.compile(block, backend=comp)
+    with torch.no_grad():
+        y, ymax = compiled(x)
+        y2, _ = compiled(x.view(B * S, D).clone().view(B, S, D))
+    torch.cuda.synchronize()
+    assert F.device_status() == 0
+    assert comp.fusion_applied and len(set(comp.launchers)) == 2, comp.declined
+    assert sum(L.launch_count for L in set(comp.launchers)) == 4
+    assert y.shape == (B, S, D) and ymax.shape == (B, S)
+    assert torch.equal(y, y2)
+    # oracle: the same chain on the flattened rows, fp32 arithmetic on the bf16-rounded values
+    f = lambda t: t.detach().float().cpu().numpy()
+    xs = f(x).reshape(B * S, D)
+    h = chain.fused_chain(xs, f(block.fc1.weight).T, [("add", f(block.fc1.bias)), ("gelu",)], "bf16")["d"]
+    want = chain.fused_chain(h, f(block.fc2.weight).T, [("add", f(block.fc2.bias)), ("add", xs)], "bf16")["d"]
+    np.testing.assert_allclose(f(y).reshape(B * S, D), want, **BF16_TOL)
+    np.testing.assert_allclose(f(ymax).reshape(-1), want.max(axis=1), **BF16_TOL)
+    torch._dynamo.reset()

@@ -196,3 +196,54 @@ def test_reference_pass_level_suite_passes_against_this_package(tmp_path):
     tail = proc.stdout.strip().splitlines()[-1] if proc.stdout.strip() else proc.stderr[-500:]
     assert proc.returncode == 0, proc.stdout[-3000:]
     assert "passed" in tail and "failed" not in tail
+
+
+def test_batched_activations_fuse_through_the_flatten_views():
+    """[B, S, D] activations: nn.Linear wraps addmm in view(x, [B*S, D]) ... view(out, [B, S, N]).
+    The chain continues through those row-regrouping views (the reference stops there:
+    fuseml/passes/fusion_pass.py:244-257), the 3-D residual lines up with the flattened tile,
+    and a reduction over the last dimension is a per-row reduction."""
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc1 = torch.nn.Linear(16, 32)
+            self.fc2 = torch.nn.Linear(32, 16)
+
+        def forward(self, x):
+            y = self.fc2(torch.nn.functional.gelu(self.fc1(x))) + x
+            return y, y.amax(-1)
+
+    from torch._functorch.aot_autograd import aot_module_simplified
+    from functorch.compile import make_boxed_func
+    seen = {}
+
+    def grab(gm, inputs):
+        seen["gm"] = gm
+        return make_boxed_func(gm.forward)
+
+    block, x = Block().eval(), torch.randn(2, 3, 16)
+    with torch.no_grad():
+        aot_module_simplified(block, (x,), fw_compiler=grab, inference_compiler=grab)(x)
+    gm = seen["gm"]
+    fpass = F.FuseMLFusionPass(gm, dag_epilogue=True, multi_reduction=True, global_reductions=True)
+    fpass._tensor_meta_from_val()
+    groups = fpass._find_fusion_groups()
+    sigs = [[s for s in g.op_signature if "view" not in s] for g in groups]
+    assert sigs == [["aten.addmm.default", "aten.gelu.default"],
+                    ["aten.addmm.default", "aten.add.Tensor", "aten.amax.default"]]
+    gen = Sm100KernelGenerator()
+    specs = [gen.build_spec(g) for g in groups]
+    assert [[N.OP_NAMES[s.opcode] for s in sp.steps] for sp in specs] == [["add_t", "gelu_erf"], ["add_t", "add_t"]]
+    assert [(r.axis, r.op) for r in specs[1].reductions] == [(1, "max")] and specs[1].store_output
+    # A of the first group is x itself (3-D): the launcher flattens it; the residual of the second is x again
+    from fuseml_b200.passes.fusion_pass import _node_shape
+    shapes = [[tuple(_node_shape(n)) for n in g.inputs] for g in groups]
+    assert (2, 3, 16) in shapes[0] and (2, 3, 16) in shapes[1]
+    # a reduction over the sequence dimension is not one the kernel runs: it stays outside the group
+    def f(x, w):
+        return torch.mm(x.view(6, 16), w).view(2, 3, 8).relu().sum(1)
+    args = (torch.randn(2, 3, 16), torch.randn(16, 8))
+    gm2 = make_fx(f)(*args)
+    ShapeProp(gm2).propagate(*args)
+    (g2,) = F.FuseMLFusionPass(gm2)._find_fusion_groups()
+    assert [s for s in g2.op_signature if "view" not in s] == ["aten.mm.default", "aten.relu.default"]
