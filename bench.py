@@ -473,8 +473,14 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the fused path has no CPU implementation")
     torch.cuda.set_device(local_rank)
     dist = None
+    numa_cores = None
     if world > 1:
         import torch.distributed as dist
+        from fuseml_b200.sharding import bind_to_device_numa
+
+        # one process per GPU, each streaming its own batch through pinned memory: keep the
+        # buffers on the GPU's own socket (N = 1 keeps every core for the CPU baseline leg)
+        numa_cores = bind_to_device_numa(local_rank)
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -581,9 +587,12 @@ def main():
                    "l2": "inputs larger than L2 (weights + activations per step exceed 126 MB"
                          + ("; weight copies rotated)" if args.workload == "cfg2" else ")"),
                    "parallelism": f"rows sharded over {world} GPU(s), weights replicated",
-                   "cuda_graph": bool(graphed)},
+                   "cuda_graph": bool(graphed),
+                   "host_affinity": (f"rank 0 bound to the {len(numa_cores)} cores NVML reports local to its GPU"
+                                     if numa_cores else "unchanged")},
         "e2e": {"value": wl.tokens * world / (e2e_ms / steps * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes, "ms_per_step": e2e_ms / steps},
+                "h2d_bytes_per_step": wl.h2d_bytes * world, "d2h_bytes_per_step": wl.d2h_bytes * world,
+                "ms_per_step": e2e_ms / steps},
         "gpu_launches": launches_timed + (steps if wl.launches_per_step > wl.gemm_launches_per_step else 0),
         "roofline": roof,
         "clocks": clocks,

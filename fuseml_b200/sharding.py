@@ -81,3 +81,36 @@ class RowShardedModule:
                 weight = x_local.shape[0] / float(global_rows) if world > 1 else 1.0
                 combined.append(allreduce_scalars(total=s.float() * weight, group=self.group)[0])
         return (y, *combined)
+
+
+def bind_to_device_numa(device_index: int, nvml=None) -> list[int] | None:
+    """Pin the calling process to the CPU cores NVML reports as local to CUDA device
+    ``device_index`` (its NUMA node), so that pinned host buffers allocated afterwards are
+    first-touched next to the GPU that copies from them.  With one process per GPU and every
+    process streaming its own batch over PCIe, buffers on the far socket make all ranks share
+    the inter-socket link.  Only the process's CPU affinity changes; nothing on the GPU is
+    set.  Returns the cores chosen, or None when NVML is not available, reports nothing, or
+    none of the reported cores is allowed to this process (the affinity is then left alone).
+    ``nvml`` is injectable for tests (an object with the pynvml functions used here)."""
+    import os
+
+    if not hasattr(os, "sched_setaffinity"):
+        return None
+    try:
+        if nvml is None:
+            import pynvml as nvml  # type: ignore[no-redef]
+        nvml.nvmlInit()
+        props = torch.cuda.get_device_properties(device_index)
+        bus_id = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        handle = nvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+        n_cpu = os.cpu_count() or 1
+        words = list(nvml.nvmlDeviceGetCpuAffinity(handle, (n_cpu + 63) // 64))
+    except Exception:
+        return None
+    local = {w * 64 + b for w, mask in enumerate(words) for b in range(64) if (int(mask) >> b) & 1}
+    allowed = os.sched_getaffinity(0)
+    chosen = sorted(local & allowed)
+    if not chosen or len(chosen) == len(allowed):
+        return None if not chosen else chosen
+    os.sched_setaffinity(0, chosen)
+    return chosen

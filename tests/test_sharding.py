@@ -81,3 +81,45 @@ def test_two_rank_gloo_matches_unsharded():
         assert m == pytest.approx(float(m_ref), rel=1e-6)
         assert mean == pytest.approx(float(y_ref.mean()), rel=1e-4, abs=1e-6)
     assert torch.allclose(rows, y_ref, rtol=1e-5, atol=1e-5)
+
+
+def test_numa_binding_uses_nvml_mask_and_respects_allowed_cores(monkeypatch):
+    """bind_to_device_numa against a fake NVML: the mask is intersected with the cores this
+    process may use; an empty intersection or a failing NVML leaves the affinity alone."""
+    import os
+    import types
+
+    from fuseml_b200 import sharding
+
+    if not hasattr(os, "sched_setaffinity"):
+        pytest.skip("no sched_setaffinity on this platform")
+    allowed = sorted(os.sched_getaffinity(0))
+    calls = []
+    monkeypatch.setattr(os, "sched_setaffinity", lambda pid, cpus: calls.append((pid, sorted(cpus))))
+    props = types.SimpleNamespace(pci_domain_id=0, pci_bus_id=0x1b, pci_device_id=0)
+    monkeypatch.setattr(sharding.torch.cuda, "get_device_properties", lambda i: props)
+
+    def fake(mask_words, seen):
+        def by_bus(b):
+            seen.append(b)
+            return "h"
+        return types.SimpleNamespace(nvmlInit=lambda: None, nvmlDeviceGetHandleByPciBusId=by_bus,
+                                     nvmlDeviceGetCpuAffinity=lambda h, n: mask_words[:n] + [0] * max(0, n - len(mask_words)))
+
+    seen: list = []
+    want = allowed[: max(1, len(allowed) // 2)]
+    words = [0] * ((max(allowed) // 64) + 1)
+    for c in want:
+        words[c // 64] |= 1 << (c % 64)
+    got = sharding.bind_to_device_numa(0, nvml=fake(words, seen))
+    assert got == want and seen == [b"00000000:1b:00.0"]
+    if len(want) < len(allowed):
+        assert calls == [(0, want)]
+    # cores outside the allowed set only: nothing changes
+    calls.clear()
+    far = [0] * ((max(allowed) // 64) + 2)
+    far[-1] = 1 << 63
+    assert sharding.bind_to_device_numa(0, nvml=fake(far, seen)) is None and calls == []
+    # NVML raising: nothing changes
+    broken = types.SimpleNamespace(nvmlInit=lambda: (_ for _ in ()).throw(RuntimeError("no driver")))
+    assert sharding.bind_to_device_numa(0, nvml=broken) is None and calls == []
