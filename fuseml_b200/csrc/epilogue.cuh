@@ -1,5 +1,5 @@
-// Epilogue virtual machine: runs a short program over 32 accumulator columns of
-// one output row held in registers.  The opcode switch is uniform across the
+// Epilogue virtual machine: runs a short program over a chunk of CH (32 or 16) accumulator
+// columns of one output row held in registers.  The opcode switch is uniform across the
 // warp (same program for every element), the element loops are fully unrolled,
 // so the interpretation overhead is a handful of instructions per op per 32
 // elements.  Semantics follow the reference's emitters
@@ -116,7 +116,7 @@ __device__ __forceinline__ float load_scalar(const void* p, int64_t idx, int32_t
   return reinterpret_cast<const float*>(p)[idx];
 }
 
-// v[i] = combine(v[i], operand[m, n0 + i]) for the 32 columns of a chunk, without a 32-element
+// v[i] = combine(v[i], operand[m, n0 + i]) for the CH columns of a chunk, without a CH-element
 // temporary: values are folded in as each 16-byte word is unpacked.  combine is a*b for MUL and
 // sa*a + sb*b otherwise (ADD: 1,1; SUB: 1,-1; RSUB: -1,1).  Columns >= N are left alone.  The
 // fast path (unit column stride, 16-byte aligned, full chunk) uses 128-bit loads; with
@@ -131,20 +131,21 @@ __device__ __forceinline__ void combine2(bool mul, f32x2 sa, f32x2 sb, float& a0
   unpack2(mul ? mul2(a, b) : fma2(sb, b, mul2(sa, a)), a0, a1);
 }
 
-__device__ __forceinline__ void fold_operand_chunk(float (&v)[kChunkN], int32_t code, const EpiOperand& o, int64_t m,
+template <int CH>
+__device__ __forceinline__ void fold_operand_chunk(float (&v)[CH], int32_t code, const EpiOperand& o, int64_t m,
                                                    int32_t n0, int32_t N) {
   const bool mul = code == FUSEML_OP_MUL_T;
   const float sa = code == FUSEML_OP_RSUB_T ? -1.0f : 1.0f;
   const float sb = code == FUSEML_OP_SUB_T ? -1.0f : 1.0f;
   const f32x2 sa2 = splat2(sa), sb2 = splat2(sb);
   const int64_t base = m * o.stride_m + static_cast<int64_t>(n0) * o.stride_n;
-  const bool full = (n0 + kChunkN <= N);
+  const bool full = (n0 + CH <= N);
   if (o.stride_n == 1 && full) {
     if (o.dtype == FUSEML_F32) {
       const float* p = reinterpret_cast<const float*>(o.ptr) + base;
       if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
 #pragma unroll
-        for (int i = 0; i < kChunkN / 4; ++i) {
+        for (int i = 0; i < CH / 4; ++i) {
           const float4 q = __ldg(reinterpret_cast<const float4*>(p) + i);
           combine2(mul, sa2, sb2, v[4 * i + 0], v[4 * i + 1], q.x, q.y);
           combine2(mul, sa2, sb2, v[4 * i + 2], v[4 * i + 3], q.z, q.w);
@@ -155,7 +156,7 @@ __device__ __forceinline__ void fold_operand_chunk(float (&v)[kChunkN], int32_t 
       const uint16_t* p = reinterpret_cast<const uint16_t*>(o.ptr) + base;
       if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
 #pragma unroll
-        for (int i = 0; i < kChunkN / 8; ++i) {
+        for (int i = 0; i < CH / 8; ++i) {
           const uint4 q = __ldg(reinterpret_cast<const uint4*>(p) + i);
           const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -171,18 +172,18 @@ __device__ __forceinline__ void fold_operand_chunk(float (&v)[kChunkN], int32_t 
     }
   }
 #pragma unroll
-  for (int i = 0; i < kChunkN; ++i) {
+  for (int i = 0; i < CH; ++i) {
     if (n0 + i < N)
       v[i] = combine(mul, sa, sb, v[i], load_scalar(o.ptr, base + static_cast<int64_t>(i) * o.stride_n, o.dtype));
   }
 }
 
-// v[i] (+|*)= src[i], src = 32 fp32 values staged in shared memory (same address for every
+// v[i] (+|*)= src[i], src = CH fp32 values staged in shared memory (same address for every
 // lane: the reads broadcast)
-template <bool kMul>
-__device__ __forceinline__ void fold_staged(float (&v)[kChunkN], const float* src) {
+template <bool kMul, int CH>
+__device__ __forceinline__ void fold_staged(float (&v)[CH], const float* src) {
 #pragma unroll
-  for (int i = 0; i < kChunkN / 4; ++i) {
+  for (int i = 0; i < CH / 4; ++i) {
     const float4 q = reinterpret_cast<const float4*>(src)[i];
     const f32x2 lo = pack2(v[4 * i + 0], v[4 * i + 1]), hi = pack2(v[4 * i + 2], v[4 * i + 3]);
     const f32x2 qlo = pack2(q.x, q.y), qhi = pack2(q.z, q.w);
@@ -191,35 +192,36 @@ __device__ __forceinline__ void fold_staged(float (&v)[kChunkN], const float* sr
   }
 }
 
-// Stores v[0..31] to row pointer `row` (element index n0 .. n0+31) in `dtype`.
+// Stores v[0..CH-1] to row pointer `row` (element index n0 .. n0+CH-1) in `dtype`.
 // fp16 saturates to +-65504 before the cast, as the reference does
 // (fuseml/codegen/kernel_generator.py:1575-1581).
+template <int CH>
 __device__ __forceinline__ void store_chunk(void* base_ptr, int64_t row_off, int32_t n0, int32_t N,
-                                            int32_t dtype, const float (&v)[kChunkN]) {
-  const bool full = (n0 + kChunkN <= N);
+                                            int32_t dtype, const float (&v)[CH]) {
+  const bool full = (n0 + CH <= N);
   if (dtype == FUSEML_F32) {
     float* p = reinterpret_cast<float*>(base_ptr) + row_off + n0;
     if (full && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
 #pragma unroll
-      for (int i = 0; i < kChunkN / 4; ++i) {
+      for (int i = 0; i < CH / 4; ++i) {
         reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < kChunkN; ++i) if (n0 + i < N) p[i] = v[i];
+      for (int i = 0; i < CH; ++i) if (n0 + i < N) p[i] = v[i];
     }
     return;
   }
-  uint32_t packed[kChunkN / 2];
+  uint32_t packed[CH / 2];
   if (dtype == FUSEML_BF16) {
 #pragma unroll
-    for (int i = 0; i < kChunkN / 2; ++i) {
+    for (int i = 0; i < CH / 2; ++i) {
       const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
       packed[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < kChunkN / 2; ++i) {
+    for (int i = 0; i < CH / 2; ++i) {
       const float a = fminf(fmaxf(v[2 * i], -65504.0f), 65504.0f);
       const float b = fminf(fmaxf(v[2 * i + 1], -65504.0f), 65504.0f);
       const __half2 h = __floats2half2_rn(a, b);
@@ -229,13 +231,13 @@ __device__ __forceinline__ void store_chunk(void* base_ptr, int64_t row_off, int
   uint16_t* p = reinterpret_cast<uint16_t*>(base_ptr) + row_off + n0;
   if (full && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
 #pragma unroll
-    for (int i = 0; i < kChunkN / 8; ++i) {
+    for (int i = 0; i < CH / 8; ++i) {
       reinterpret_cast<uint4*>(p)[i] =
           make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < kChunkN; ++i) {
+    for (int i = 0; i < CH; ++i) {
       if (n0 + i < N) p[i] = static_cast<uint16_t>((packed[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu);
     }
   }
@@ -245,42 +247,42 @@ __device__ __forceinline__ void store_chunk(void* base_ptr, int64_t row_off, int
 // operand loads and aux stores are skipped (values are don't-care).
 // `staged` points at this chunk's 32 columns of the row vectors staged in shared memory
 // (vector j at staged + j * staged_stride).
-template <bool kUsesSaved>
+template <bool kUsesSaved, int CH>
 __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int32_t n0, bool row_ok,
-                                            float (&v)[kChunkN], const float* staged, int32_t staged_stride) {
-  float s[kUsesSaved ? kChunkN : 1];
+                                            float (&v)[CH], const float* staged, int32_t staged_stride) {
+  float s[kUsesSaved ? CH : 1];
   if (kUsesSaved) {
 #pragma unroll
-    for (int i = 0; i < (kUsesSaved ? kChunkN : 1); ++i) s[i] = 0.0f;
+    for (int i = 0; i < (kUsesSaved ? CH : 1); ++i) s[i] = 0.0f;
   }
   for (int op = 0; op < p.n_ops; ++op) {
     const int32_t code = p.ops[op].opcode;
     switch (code) {
       case FUSEML_OP_RELU:
 #pragma unroll
-        for (int i = 0; i < kChunkN; ++i) v[i] = v[i] > 0.0f ? v[i] : 0.0f;
+        for (int i = 0; i < CH; ++i) v[i] = v[i] > 0.0f ? v[i] : 0.0f;
         break;
       case FUSEML_OP_GELU_ERF:
 #pragma unroll
-        for (int i = 0; i < kChunkN; i += 2) gelu_erf2(v[i], v[i + 1]);
+        for (int i = 0; i < CH; i += 2) gelu_erf2(v[i], v[i + 1]);
         break;
       case FUSEML_OP_GELU_TANH:
 #pragma unroll
-        for (int i = 0; i < kChunkN; i += 2) gelu_tanh2(v[i], v[i + 1]);
+        for (int i = 0; i < CH; i += 2) gelu_tanh2(v[i], v[i + 1]);
         break;
       case FUSEML_OP_SIGMOID:
 #pragma unroll
-        for (int i = 0; i < kChunkN; i += 2) sigmoid2(v[i], v[i + 1]);
+        for (int i = 0; i < CH; i += 2) sigmoid2(v[i], v[i + 1]);
         break;
       case FUSEML_OP_ADD_IMM: {
         const float c = p.ops[op].imm;
 #pragma unroll
-        for (int i = 0; i < kChunkN; i += 2) unpack2(add2(pack2(v[i], v[i + 1]), splat2(c)), v[i], v[i + 1]);
+        for (int i = 0; i < CH; i += 2) unpack2(add2(pack2(v[i], v[i + 1]), splat2(c)), v[i], v[i + 1]);
       } break;
       case FUSEML_OP_MUL_IMM: {
         const float c = p.ops[op].imm;
 #pragma unroll
-        for (int i = 0; i < kChunkN; i += 2) unpack2(mul2(pack2(v[i], v[i + 1]), splat2(c)), v[i], v[i + 1]);
+        for (int i = 0; i < CH; i += 2) unpack2(mul2(pack2(v[i], v[i + 1]), splat2(c)), v[i], v[i + 1]);
       } break;
       case FUSEML_OP_ADD_T:
       case FUSEML_OP_MUL_T:
@@ -289,40 +291,40 @@ __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int3
         const int32_t pre = p.ops[op].reserved;
         if (pre == 1 || pre == 2) {
           const float* src = staged + (pre - 1) * staged_stride;
-          if (code == FUSEML_OP_ADD_T) fold_staged<false>(v, src); else fold_staged<true>(v, src);
+          if (code == FUSEML_OP_ADD_T) fold_staged<false, CH>(v, src); else fold_staged<true, CH>(v, src);
         } else if (row_ok) {
-          fold_operand_chunk(v, code, p.operands[p.ops[op].slot], m, n0, p.N);
+          fold_operand_chunk<CH>(v, code, p.operands[p.ops[op].slot], m, n0, p.N);
         }
       } break;
       case FUSEML_OP_STORE_AUX: {
         if (row_ok) {
           const EpiOperand& o = p.operands[p.ops[op].slot];
-          store_chunk(const_cast<void*>(o.ptr), m * o.stride_m, n0, p.N, o.dtype, v);
+          store_chunk<CH>(const_cast<void*>(o.ptr), m * o.stride_m, n0, p.N, o.dtype, v);
         }
       } break;
       case FUSEML_OP_SAVE:
         if (kUsesSaved) {
 #pragma unroll
-          for (int i = 0; i < kChunkN; ++i) s[i] = v[i];
+          for (int i = 0; i < CH; ++i) s[i] = v[i];
         }
         break;
       case FUSEML_OP_SWAP:
         if (kUsesSaved) {
 #pragma unroll
-          for (int i = 0; i < kChunkN; ++i) { const float x = v[i]; v[i] = s[i]; s[i] = x; }
+          for (int i = 0; i < CH; ++i) { const float x = v[i]; v[i] = s[i]; s[i] = x; }
         }
         break;
       case FUSEML_OP_ADD_SAVED:
         if (kUsesSaved) {
 #pragma unroll
-          for (int i = 0; i < kChunkN; i += 2)
+          for (int i = 0; i < CH; i += 2)
             unpack2(add2(pack2(v[i], v[i + 1]), pack2(s[i], s[i + 1])), v[i], v[i + 1]);
         }
         break;
       case FUSEML_OP_MUL_SAVED:
         if (kUsesSaved) {
 #pragma unroll
-          for (int i = 0; i < kChunkN; i += 2)
+          for (int i = 0; i < CH; i += 2)
             unpack2(mul2(pack2(v[i], v[i + 1]), pack2(s[i], s[i + 1])), v[i], v[i + 1]);
         }
         break;

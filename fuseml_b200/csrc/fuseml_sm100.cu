@@ -60,11 +60,11 @@ static int encode_2d(CUtensorMap* tm, int32_t dtype, const void* base, int64_t r
   return r == CUDA_SUCCESS ? FUSEML_OK : FUSEML_E_LAYOUT;
 }
 
-template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED, int CG>
+template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED, int CG, int EW>
 static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
                            cudaStream_t stream) {
   using L = v2::Smem<BN, STAGES, CG>;
-  auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, FMT, B_MN, SAVED, CG>;
+  auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, FMT, B_MN, SAVED, CG, EW>;
   static int configured_device = -1;   // per instantiation; the attribute is sticky per device function
   static int max_clusters = 0;
   int dev = 0;
@@ -79,7 +79,7 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const G
       // how many CTA pairs the device can hold at once (GPCs with an odd SM count lose one SM)
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3(2 * 148);
-      q.blockDim = dim3(v2::kThreads);
+      q.blockDim = dim3(v2::threads_for(EW));
       q.dynamicSmemBytes = L::kDynamicBytes;
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -110,7 +110,7 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const G
   }
   cfg.attrs = attr; cfg.numAttrs = n_attr;
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(v2::kThreads);
+  cfg.blockDim = dim3(v2::threads_for(EW));
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
@@ -118,13 +118,13 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const G
   return FUSEML_OK;
 }
 
-template <int BN, int STAGES, int CG>
+template <int BN, int STAGES, int CG, int EW = 8>
 static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int fmt, bool b_mn,
                      int grid, cudaStream_t stream) {
   const bool saved = p.uses_saved != 0;
 #define FUSEML_DISPATCH(F, MN)                                                              \
-  return saved ? launch_instance<BN, STAGES, F, MN, true, CG>(ta, tb, p, grid, stream)      \
-               : launch_instance<BN, STAGES, F, MN, false, CG>(ta, tb, p, grid, stream)
+  return saved ? launch_instance<BN, STAGES, F, MN, true, CG, EW>(ta, tb, p, grid, stream)  \
+               : launch_instance<BN, STAGES, F, MN, false, CG, EW>(ta, tb, p, grid, stream)
   if (fmt == 2) { FUSEML_DISPATCH(2, false); }
   if (fmt == 1) { if (b_mn) { FUSEML_DISPATCH(1, true); } else { FUSEML_DISPATCH(1, false); } }
   if (b_mn) { FUSEML_DISPATCH(0, true); } else { FUSEML_DISPATCH(0, false); }
@@ -348,7 +348,13 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     grid = std::min<int>(grid, static_cast<int>(w.partials));
     fill_neutral_kernel<<<1, 256, 0, stream>>>(p.red_sum, p.red_max, static_cast<int>(w.partials));
   }
-  if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, p, fmt, b_mn, grid, stream);
+  // A launch in which no CTA gets a second tile has nothing to overlap its epilogue with: run it
+  // with sixteen epilogue warps on 16-column chunks (twice the warps in flight for the operand
+  // loads, the special-function unit and the stores).  Reductions keep the 8-warp instance
+  // (their partial layout is sized for two warps per row).
+  const bool lone_tile = p.num_tiles * CGr <= grid && p.red_kinds == 0 && fmt != 2;
+  if (CGr == 2 && lone_tile) rc = launch_bn<256, 6, 2, 16>(ta, tb, p, fmt, b_mn, grid, stream);
+  else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, p, fmt, b_mn, grid, stream);
   else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, p, fmt, b_mn, grid, stream);
   else rc = launch_bn<128, 6, 1>(ta, tb, p, fmt, b_mn, grid, stream);
   if (rc != FUSEML_OK) return rc;

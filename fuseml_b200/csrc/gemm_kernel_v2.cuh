@@ -22,9 +22,10 @@
 namespace fuseml {
 namespace v2 {
 
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = 64 + kEpiWarps * 32;  // 320
-constexpr int kEpiSplit = 2;                   // warps sharing one TMEM lane quarter
+// Epilogue warps per CTA: 8 (two per TMEM lane quarter, 32-column chunks) or 16 (four per
+// quarter, 16-column chunks: half the registers per thread, twice the warps to hide the latency
+// of an epilogue that nothing overlaps - a CTA's only tile).
+constexpr int threads_for(int epi_warps) { return 64 + epi_warps * 32; }   // 320 or 576
 
 enum : int32_t {
   kWhereProducerEmpty = 0x201,
@@ -119,8 +120,8 @@ __device__ __forceinline__ void prefetch_operands(const GemmParams& p, int64_t m
 
 // FMT: 0 = f16, 1 = bf16, 2 = tf32 (fp32 storage).  B_MN: B is row-major [K,N] in global
 // memory (MN-major tiles) instead of K-major.  CG: CTAs per tile (1 or 2).
-template <int BN, int STAGES, int FMT, bool B_MN, bool USES_SAVED, int CG>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int STAGES, int FMT, bool B_MN, bool USES_SAVED, int CG, int EW>
+__global__ void __launch_bounds__(threads_for(EW), 1)
 gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ GemmParams p) {
   using L = Smem<BN, STAGES, CG>;
@@ -130,6 +131,10 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   constexpr int kKSteps = BK / UMMA_K;
   constexpr int BN_CTA = BN / CG;                 // most B columns one CTA loads (sizes shared memory)
   constexpr uint32_t kTmemCols = 2 * BN;
+  static_assert(EW == 8 || EW == 16, "two or four epilogue warps per TMEM lane quarter");
+  constexpr int kEpiWarps = EW;
+  constexpr int kEpiSplit = EW / 4;             // warps sharing one TMEM lane quarter
+  constexpr int CH = (EW == 16) ? 16 : 32;      // accumulator columns per chunk
   static_assert(!(B_MN && FMT == 2), "MN-major B is only wired for 16-bit operands");
   static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair");
   static_assert(!B_MN || (BN_CTA % 64 == 0), "MN-major B is loaded in 64-column boxes");
@@ -414,7 +419,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
               staged[j * BN + idx] = n < p.N ? epi::load_scalar(p.operands[slot].ptr, n, p.operands[slot].dtype) : 0.0f;
           }
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        asm volatile("bar.sync 2, %0;" ::"n"(32 * EW) : "memory");
       }
       // After a failed wait the warp keeps walking its tiles without touching TMEM, so that the
       // named barriers below still see all eight warps.
@@ -429,8 +434,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       ptx::tc_fence_after_sync();
       float row_sum = 0.0f, row_max = -INFINITY;
 #pragma unroll 1
-      for (int c = half; ok && c < bn / kChunkN; c += kEpiSplit) {
-        const int32_t n0 = n_tile0 + c * kChunkN;
+      for (int c = half; ok && c < bn / CH; c += kEpiSplit) {
+        const int32_t n0 = n_tile0 + c * CH;
         if (n0 >= p.N) break;  // uniform across the warp
         // Pull this thread's 64-byte slices of the matrix operand (residual) for this chunk and
         // for the warp's next one into L1 now: by the time the program reaches the op, the
@@ -438,38 +443,42 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (p.mat_slot >= 0 && row_ok) {
           const EpiOperand& mo = p.operands[p.mat_slot];
           const char* mp = reinterpret_cast<const char*>(mo.ptr) + (static_cast<int64_t>(m) * mo.stride_m + n0) * 2;
-          if (c == half) { ptx::prefetch_l1(mp); ptx::prefetch_l1(mp + 63); }
-          if (n0 + kEpiSplit * kChunkN < p.N) {
-            ptx::prefetch_l1(mp + kEpiSplit * kChunkN * 2);
-            ptx::prefetch_l1(mp + kEpiSplit * kChunkN * 2 + 63);
+          if (c == half) { ptx::prefetch_l1(mp); ptx::prefetch_l1(mp + 2 * CH - 1); }
+          if (n0 + kEpiSplit * CH < p.N) {
+            ptx::prefetch_l1(mp + kEpiSplit * CH * 2);
+            ptx::prefetch_l1(mp + kEpiSplit * CH * 2 + 2 * CH - 1);
           }
         }
-        uint32_t r[kChunkN];
-        ptx::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(acc * BN + c * kChunkN), r);
+        uint32_t r[CH];
+        ptx::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(acc * BN + c * CH), r);
         ptx::tmem_ld_wait();
-        float v[kChunkN];
+        float v[CH];
 #pragma unroll
-        for (int i = 0; i < kChunkN; ++i) v[i] = __uint_as_float(r[i]);
-        epi::run_program<USES_SAVED>(p, m, n0, row_ok, v, staged + c * kChunkN, BN);
+        for (int i = 0; i < CH; ++i) v[i] = __uint_as_float(r[i]);
+        epi::run_program<USES_SAVED, CH>(p, m, n0, row_ok, v, staged + c * CH, BN);
         if (p.d != nullptr && row_ok) {
-          epi::store_chunk(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
+          epi::store_chunk<CH>(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
         }
         if (red_any) {
           if (p.red_axis == FUSEML_AXIS_M) {
-            float vs[kChunkN], vm[kChunkN];
+            // column reductions transpose 32 x 32 blocks in registers: 32-column chunks only (the
+            // host never picks the 16-warp instance for them)
+            if constexpr (CH == 32) {
+              float vs[CH], vm[CH];
 #pragma unroll
-            for (int i = 0; i < kChunkN; ++i) {
-              vs[i] = row_ok ? v[i] : 0.0f;
-              vm[i] = row_ok ? v[i] : -INFINITY;
+              for (int i = 0; i < CH; ++i) {
+                vs[i] = row_ok ? v[i] : 0.0f;
+                vm[i] = row_ok ? v[i] : -INFINITY;
+              }
+              if (red_sum) colred[(quarter * 2 + 0) * BN + c * CH + lane] = warp_column_reduce<false>(vs, lane);
+              if (red_max) colred[(quarter * 2 + 1) * BN + c * CH + lane] = warp_column_reduce<true>(vm, lane);
             }
-            if (red_sum) colred[(quarter * 2 + 0) * BN + c * kChunkN + lane] = warp_column_reduce<false>(vs, lane);
-            if (red_max) colred[(quarter * 2 + 1) * BN + c * kChunkN + lane] = warp_column_reduce<true>(vm, lane);
-          } else if (n0 + kChunkN <= p.N) {
+          } else if (n0 + CH <= p.N) {
             // full chunk: pairwise packed adds (two chains), maxima as a tree
             epi::f32x2 s0 = epi::pack2(v[0], v[1]), s1 = epi::pack2(v[2], v[3]);
             float m0 = fmaxf(v[0], v[1]), m1 = fmaxf(v[2], v[3]);
 #pragma unroll
-            for (int i = 4; i < kChunkN; i += 4) {
+            for (int i = 4; i < CH; i += 4) {
               s0 = epi::add2(s0, epi::pack2(v[i], v[i + 1]));
               s1 = epi::add2(s1, epi::pack2(v[i + 2], v[i + 3]));
               m0 = fmaxf(m0, fmaxf(v[i], v[i + 1]));
@@ -481,7 +490,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             row_max = fmaxf(row_max, fmaxf(m0, m1));
           } else {
 #pragma unroll
-            for (int i = 0; i < kChunkN; ++i) {
+            for (int i = 0; i < CH; ++i) {
               const bool in = (n0 + i < p.N);
               row_sum += in ? v[i] : 0.0f;
               row_max = in ? fmaxf(row_max, v[i]) : row_max;
@@ -515,7 +524,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           }
         } else {
           // AXIS_M: combine the four quarters' column partials, one thread per column
-          asm volatile("bar.sync 1, 256;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
           for (int j = threadIdx.x - 64; j < bn; j += kEpiWarps * 32) {
             const int32_t n = n_tile0 + j;
             if (n < p.N && ok && tm128 * kTileM < p.M) {
@@ -527,7 +536,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
                                      fmaxf(colred[5 * BN + j], colred[7 * BN + j]));
             }
           }
-          asm volatile("bar.sync 1, 256;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
         }
       }
     }
@@ -547,7 +556,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         colred[ew * 2 + 0] = ws;
         colred[ew * 2 + 1] = wm;
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
       if (threadIdx.x == 64) {
         float s = 0.0f, mx = -INFINITY;
         for (int w = 0; w < kEpiWarps; ++w) { s += colred[w * 2]; mx = fmaxf(mx, colred[w * 2 + 1]); }

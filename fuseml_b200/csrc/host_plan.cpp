@@ -197,6 +197,16 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
     best = std::max(waves * 2.0 * 256.0 * 256.0 * static_cast<double>(k_pad) / (2.0 * per_sm_rate) * 1e6,
                     plan->t_hbm_us);
   }
+  // One row of tiles (M <= 128: decode-sized batches, small fp32 problems) and fewer tiles than
+  // SMs: a 256-wide tile would leave most of the machine idle while a few CTAs walk the whole
+  // K loop.  Narrow the tiles (multiples of 32 columns) until there is about one per SM: the
+  // operand stream is then pulled by every SM, and each CTA's K loop issues proportionally
+  // smaller MMAs.
+  if (plan->cluster == 1 && tiles_m == 1 && d->N > 32) {
+    const int64_t per_sm = (d->N + props.sm_count - 1) / std::max(1, props.sm_count);
+    const int64_t width = std::min<int64_t>(256, std::max<int64_t>(32, round_up(per_sm, 32)));
+    if (width < best_bn) best_bn = static_cast<int>(width);
+  }
   plan->tile_n = best_bn;
   const int cg = plan->cluster;
   const int64_t tiles_n = (d->N + best_bn - 1) / best_bn;

@@ -112,7 +112,8 @@ def test_plan_budgets_and_bounds(native_lib):
     assert rc == N.OK and p.bound == 0 and p.t_hbm_us > p.t_tensor_us
     # tiny problem: latency-bound, still fused (single tier: no bypass)
     rc, p = _plan(native_lib, _desc(128, 512, 2048))
-    assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.grid <= 4 * 2 and p.cluster == 1
+    # one row of tiles: narrowed to 32 columns so that 16 CTAs share the K loop instead of 2
+    assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.cluster == 1 and (p.tile_n, p.grid) == (32, 16)
 
 
 def test_plan_follows_device_props(native_lib):

@@ -183,7 +183,7 @@ def test_tile_widths_and_cta_pairs(K, b_view):
     b = (torch.randn(256, 1000, generator=g) / 16).to(torch.bfloat16)
     b = b.cuda() if b_view == "n" else b.t().contiguous().cuda().t()
     ref = (a.float() @ b.float()).cpu().numpy()
-    for tile_n, cluster in ((64, 1), (128, 1), (256, 1), (160, 2), (192, 2), (224, 2), (256, 2)):
+    for tile_n, cluster in ((32, 1), (64, 1), (96, 1), (128, 1), (256, 1), (160, 2), (192, 2), (224, 2), (256, 2)):
         out = torch.full((600, 1000), float("nan"), dtype=torch.bfloat16, device="cuda")
         desc = N.GemmDesc()
         K.fill_desc(desc, a, b, None, out, torch.bfloat16)
