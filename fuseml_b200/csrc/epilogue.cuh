@@ -192,6 +192,40 @@ __device__ __forceinline__ void fold_staged(float (&v)[CH], const float* src) {
   }
 }
 
+// The 16 columns of one row of a 128 x 64 box of 16-bit values in shared memory, 128-byte
+// swizzle: `piece` points at the first 16-byte piece, the second one sits at piece ^ 16.
+__device__ __forceinline__ void fold_tile_smem(float (&v)[16], bool mul, const uint8_t* piece, int32_t dtype) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<uintptr_t>(piece) ^ (h ? 16u : 0u));
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f;
+      if (dtype == FUSEML_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+      else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      const f32x2 a = pack2(v[8 * h + 2 * j], v[8 * h + 2 * j + 1]), b = pack2(f.x, f.y);
+      unpack2(mul ? mul2(a, b) : add2(a, b), v[8 * h + 2 * j], v[8 * h + 2 * j + 1]);
+    }
+  }
+}
+__device__ __forceinline__ void store_tile_smem(const float (&v)[16], uint8_t* piece, int32_t dtype) {
+  uint32_t packed[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (dtype == FUSEML_BF16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __half2 h = __floats2half2_rn(fminf(fmaxf(v[2 * i], -65504.0f), 65504.0f),
+                                          fminf(fmaxf(v[2 * i + 1], -65504.0f), 65504.0f));
+      packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  *reinterpret_cast<uint4*>(piece) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(piece) ^ 16u) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+}
+
 // Stores v[0..CH-1] to row pointer `row` (element index n0 .. n0+CH-1) in `dtype`.
 // fp16 saturates to +-65504 before the cast, as the reference does
 // (fuseml/codegen/kernel_generator.py:1575-1581).
@@ -245,11 +279,13 @@ __device__ __forceinline__ void store_chunk(void* base_ptr, int64_t row_off, int
 
 // Runs the program on one chunk.  `row_ok` is false for rows past M: their
 // operand loads and aux stores are skipped (values are don't-care).
-// `staged` points at this chunk's 32 columns of the row vectors staged in shared memory
-// (vector j at staged + j * staged_stride).
+// `staged` points at this chunk's columns of the row vectors staged in shared memory
+// (vector j at staged + j * staged_stride); `mat_piece`, when not null, at this thread's 16
+// columns of the matrix operand in a swizzled shared-memory box (ops with reserved == 3).
 template <bool kUsesSaved, int CH>
 __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int32_t n0, bool row_ok,
-                                            float (&v)[CH], const float* staged, int32_t staged_stride) {
+                                            float (&v)[CH], const float* staged, int32_t staged_stride,
+                                            const uint8_t* mat_piece = nullptr) {
   float s[kUsesSaved ? CH : 1];
   if (kUsesSaved) {
 #pragma unroll
@@ -292,6 +328,9 @@ __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int3
         if (pre == 1 || pre == 2) {
           const float* src = staged + (pre - 1) * staged_stride;
           if (code == FUSEML_OP_ADD_T) fold_staged<false, CH>(v, src); else fold_staged<true, CH>(v, src);
+        } else if (pre == 3 && mat_piece != nullptr) {
+          // this thread's slice of the matrix operand, brought into shared memory by TMA
+          if constexpr (CH == 16) fold_tile_smem(v, code == FUSEML_OP_MUL_T, mat_piece, p.operands[p.ops[op].slot].dtype);
         } else if (row_ok) {
           fold_operand_chunk<CH>(v, code, p.operands[p.ops[op].slot], m, n0, p.N);
         }

@@ -61,8 +61,8 @@ static int encode_2d(CUtensorMap* tm, int32_t dtype, const void* base, int64_t r
 }
 
 template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED, int CG, int EW>
-static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                           cudaStream_t stream) {
+static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tr, const CUtensorMap& td,
+                           const GemmParams& p, int grid, cudaStream_t stream) {
   using L = v2::Smem<BN, STAGES, CG>;
   auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, FMT, B_MN, SAVED, CG, EW>;
   static int configured_device = -1;   // per instantiation; the attribute is sticky per device function
@@ -113,18 +113,18 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const G
   cfg.blockDim = dim3(v2::threads_for(EW));
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tr, td, p);
   if (e != cudaSuccess) { cudaGetLastError(); return FUSEML_E_LAUNCH; }
   return FUSEML_OK;
 }
 
 template <int BN, int STAGES, int CG, int EW = 8>
-static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int fmt, bool b_mn,
-                     int grid, cudaStream_t stream) {
+static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tr, const CUtensorMap& td,
+                     const GemmParams& p, int fmt, bool b_mn, int grid, cudaStream_t stream) {
   const bool saved = p.uses_saved != 0;
 #define FUSEML_DISPATCH(F, MN)                                                              \
-  return saved ? launch_instance<BN, STAGES, F, MN, true, CG, EW>(ta, tb, p, grid, stream)  \
-               : launch_instance<BN, STAGES, F, MN, false, CG, EW>(ta, tb, p, grid, stream)
+  return saved ? launch_instance<BN, STAGES, F, MN, true, CG, EW>(ta, tb, tr, td, p, grid, stream)  \
+               : launch_instance<BN, STAGES, F, MN, false, CG, EW>(ta, tb, tr, td, p, grid, stream)
   if (fmt == 2) { FUSEML_DISPATCH(2, false); }
   if (fmt == 1) { if (b_mn) { FUSEML_DISPATCH(1, true); } else { FUSEML_DISPATCH(1, false); } }
   if (b_mn) { FUSEML_DISPATCH(0, true); } else { FUSEML_DISPATCH(0, false); }
@@ -353,10 +353,26 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   // loads, the special-function unit and the stores).  Reductions keep the 8-warp instance
   // (their partial layout is sized for two warps per row).
   const bool lone_tile = p.num_tiles * CGr <= grid && p.red_kinds == 0 && fmt != 2;
-  if (CGr == 2 && lone_tile) rc = launch_bn<256, 6, 2, 16>(ta, tb, p, fmt, b_mn, grid, stream);
-  else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, p, fmt, b_mn, grid, stream);
-  else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, p, fmt, b_mn, grid, stream);
-  else rc = launch_bn<128, 6, 1>(ta, tb, p, fmt, b_mn, grid, stream);
+  CUtensorMap tr, td;
+  std::memset(&tr, 0, sizeof(tr));
+  std::memset(&td, 0, sizeof(td));
+  if (CGr == 2 && lone_tile && BN == 256) {
+    // Tile I/O through shared memory: the matrix operand (residual) and the output tile move
+    // as 128 x 64 boxes by TMA instead of row-per-thread accesses.  16-bit types, 16-byte
+    // aligned base and row pitch (what a tensor map needs); anything else keeps the direct path.
+    if (p.mat_slot >= 0) {
+      const EpiOperand& mo = p.operands[p.mat_slot];
+      if (encode_2d(&tr, mo.dtype, mo.ptr, desc->M, desc->N, mo.stride_m, 64, kTileM) == FUSEML_OK) p.io_flags |= 1;
+    }
+    if (p.d != nullptr && (p.out_dtype == FUSEML_BF16 || p.out_dtype == FUSEML_F16) &&
+        (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0 && (p.ldd * 2) % 16 == 0 &&
+        encode_2d(&td, p.out_dtype, p.d, desc->M, desc->N, p.ldd, 64, kTileM) == FUSEML_OK) {
+      p.io_flags |= 2;
+    }
+    rc = launch_bn<256, 6, 2, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
+  } else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
+  else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
+  else rc = launch_bn<128, 6, 1>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
   if (rc != FUSEML_OK) return rc;
 
   if (desc->reduce.kinds != 0) {

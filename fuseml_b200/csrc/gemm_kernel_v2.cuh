@@ -33,6 +33,7 @@ enum : int32_t {
   kWhereMmaTmemEmpty = 0x203,
   kWhereEpilogueTmemFull = 0x204,
   kWhereProducerDrain = 0x205,
+  kWhereEpilogueTileIn = 0x206,
 };
 
 // Optional stall counters (diagnostic builds only, -DFUSEML_STALL_COUNTERS): per CTA
@@ -60,7 +61,7 @@ struct Smem {
   static constexpr int kColRedBytes = 4 * 2 * BN * 4;             // [quarter][sum|max][BN]
   static constexpr int kStagedBytes = 2 * 2 * BN * 4;             // [acc buffer][row vector][BN] fp32
   static constexpr int kBarOffset = kRingBytes + kColRedBytes + kStagedBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kNumBars = 2 * STAGES + 5;                 // ring full/empty, TMEM full/empty x 2, tile I/O
   static constexpr int kTotalBytes = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kDynamicBytes = kTotalBytes + 1024;
 };
@@ -123,6 +124,7 @@ __device__ __forceinline__ void prefetch_operands(const GemmParams& p, int64_t m
 template <int BN, int STAGES, int FMT, bool B_MN, bool USES_SAVED, int CG, int EW>
 __global__ void __launch_bounds__(threads_for(EW), 1)
 gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_d,
                         const __grid_constant__ GemmParams p) {
   using L = Smem<BN, STAGES, CG>;
   constexpr int kElemBytes = (FMT == 2) ? 4 : 2;
@@ -132,6 +134,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   constexpr int BN_CTA = BN / CG;                 // most B columns one CTA loads (sizes shared memory)
   constexpr uint32_t kTmemCols = 2 * BN;
   static_assert(EW == 8 || EW == 16, "two or four epilogue warps per TMEM lane quarter");
+  static_assert(EW == 8 || L::kStageBytes == 2 * kTileM * kSwizzleBytes, "tile I/O packs two boxes per ring stage");
   constexpr int kEpiWarps = EW;
   constexpr int kEpiSplit = EW / 4;             // warps sharing one TMEM lane quarter
   constexpr int CH = (EW == 16) ? 16 : 32;      // accumulator columns per chunk
@@ -148,6 +151,14 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tile_in_bar = bar_base + 8u * (2 * STAGES + 4);
+  // tile I/O through the drained ring (sixteen-warp instance only; see GemmParams::io_flags)
+  // (only when every tile walker really has at most one tile: the launch may have been given
+  // fewer CTA pairs than the host asked for)
+  const bool lone_tile = p.num_tiles <= static_cast<int32_t>(gridDim.x) / CG;
+  const bool tile_in = (EW == 16) && lone_tile && (p.io_flags & 1) != 0;
+  const bool tile_out = (EW == 16) && lone_tile && (p.io_flags & 2) != 0;
+  constexpr int kBoxBytes = kTileM * kSwizzleBytes;   // 128 rows x 64 16-bit columns
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   float* colred = reinterpret_cast<float*>(smem + L::kRingBytes);
@@ -172,12 +183,15 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       ptx::mbar_init(tmem_full_bar(a), 1);
       ptx::mbar_init(tmem_empty_bar(a), kEpiWarps * CG);   // leader collects both CTAs' epilogue warps
     }
+    ptx::mbar_init(tile_in_bar, 1);
     *abort_flag = 0u;
     ptx::fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
+    if (tile_in) ptx::prefetch_tensormap(&tmap_r);
+    if (tile_out) ptx::prefetch_tensormap(&tmap_d);
   }
   if (warp == 1) {
     if (CG == 2) {
@@ -275,6 +289,28 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             }
           }
           ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (EW == 16 && tile_in && ok && unit < p.num_tiles) {
+        // This CTA's only tile: as the last MMAs drain the ring, bring the tile of the matrix
+        // operand (residual) into the freed stages, boxes 0,1 -> stage 0, boxes 2,3 -> stage 1
+        // (a stage holds 32 KB, a box of 128 rows x 64 columns 16 KB).
+        int32_t tm, tn;
+        tile_coords(unit, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
+        const int32_t m0 = tm * (kTileM * CG) + static_cast<int32_t>(cta_rank) * kTileM;
+        const int32_t n_tile0 = tn * bn;
+        ptx::mbar_arrive_expect_tx(tile_in_bar, 4 * kBoxBytes);
+        for (int i = 0; i < STAGES && ok; ++i) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWhereProducerEmpty)) {
+            ok = false;
+            break;
+          }
+          if (stage < 2) {
+            const uint32_t dst = smem_base + stage * L::kStageBytes;
+            ptx::tma_load_2d(dst, &tmap_r, tile_in_bar, n_tile0 + stage * 128, m0);
+            ptx::tma_load_2d(dst + kBoxBytes, &tmap_r, tile_in_bar, n_tile0 + stage * 128 + 64, m0);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -433,71 +469,97 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       FUSEML_STALL_T0();
       ptx::tc_fence_after_sync();
       float row_sum = 0.0f, row_max = -INFINITY;
+      // Tile I/O through shared memory (see GemmParams::io_flags): every warp then walks all its
+      // chunks, active or not, because each 64-column box ends in a barrier of all epilogue warps.
+      const bool staged_io = tile_in || tile_out;
+      if (tile_in && ok &&
+          !ptx::mbar_wait(tile_in_bar, 0u, abort_flag, p.status, kWhereEpilogueTileIn, true)) {
+        ok = false;
+      }
 #pragma unroll 1
-      for (int c = half; ok && c < bn / CH; c += kEpiSplit) {
+      for (int c = half; (ok || staged_io) && c < bn / CH; c += kEpiSplit) {
         const int32_t n0 = n_tile0 + c * CH;
-        if (n0 >= p.N) break;  // uniform across the warp
-        // Pull this thread's 64-byte slices of the matrix operand (residual) for this chunk and
-        // for the warp's next one into L1 now: by the time the program reaches the op, the
-        // load hits L1 instead of waiting on L2.  Costs no registers.
-        if (p.mat_slot >= 0 && row_ok) {
-          const EpiOperand& mo = p.operands[p.mat_slot];
-          const char* mp = reinterpret_cast<const char*>(mo.ptr) + (static_cast<int64_t>(m) * mo.stride_m + n0) * 2;
-          if (c == half) { ptx::prefetch_l1(mp); ptx::prefetch_l1(mp + 2 * CH - 1); }
-          if (n0 + kEpiSplit * CH < p.N) {
-            ptx::prefetch_l1(mp + kEpiSplit * CH * 2);
-            ptx::prefetch_l1(mp + kEpiSplit * CH * 2 + 2 * CH - 1);
+        const bool active = ok && n0 < p.N;   // uniform across the warp
+        if (!active && !staged_io) break;
+        // this thread's 16 columns inside the swizzled 128 x 64 box (box = chunk / 4)
+        uint8_t* piece = smem + (c >> 2) * kBoxBytes + (quarter * 32 + lane) * kSwizzleBytes +
+                         ((((c & 3) * 2) ^ (lane & 7)) << 4);
+        if (active) {
+          // Pull this thread's 64-byte slices of the matrix operand (residual) for this chunk and
+          // for the warp's next one into L1 now: by the time the program reaches the op, the
+          // load hits L1 instead of waiting on L2.  Costs no registers.
+          if (p.mat_slot >= 0 && row_ok && !tile_in) {
+            const EpiOperand& mo = p.operands[p.mat_slot];
+            const char* mp = reinterpret_cast<const char*>(mo.ptr) + (static_cast<int64_t>(m) * mo.stride_m + n0) * 2;
+            if (c == half) { ptx::prefetch_l1(mp); ptx::prefetch_l1(mp + 2 * CH - 1); }
+            if (n0 + kEpiSplit * CH < p.N) {
+              ptx::prefetch_l1(mp + kEpiSplit * CH * 2);
+              ptx::prefetch_l1(mp + kEpiSplit * CH * 2 + 2 * CH - 1);
+            }
           }
-        }
-        uint32_t r[CH];
-        ptx::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(acc * BN + c * CH), r);
-        ptx::tmem_ld_wait();
-        float v[CH];
-#pragma unroll
-        for (int i = 0; i < CH; ++i) v[i] = __uint_as_float(r[i]);
-        epi::run_program<USES_SAVED, CH>(p, m, n0, row_ok, v, staged + c * CH, BN);
-        if (p.d != nullptr && row_ok) {
-          epi::store_chunk<CH>(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
-        }
-        if (red_any) {
-          if (p.red_axis == FUSEML_AXIS_M) {
-            // column reductions transpose 32 x 32 blocks in registers: 32-column chunks only (the
-            // host never picks the 16-warp instance for them)
-            if constexpr (CH == 32) {
-              float vs[CH], vm[CH];
-#pragma unroll
-              for (int i = 0; i < CH; ++i) {
-                vs[i] = row_ok ? v[i] : 0.0f;
-                vm[i] = row_ok ? v[i] : -INFINITY;
+          uint32_t r[CH];
+          ptx::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(acc * BN + c * CH), r);
+          ptx::tmem_ld_wait();
+          float v[CH];
+  #pragma unroll
+          for (int i = 0; i < CH; ++i) v[i] = __uint_as_float(r[i]);
+          epi::run_program<USES_SAVED, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
+          if (tile_out) {
+            if constexpr (CH == 16) epi::store_tile_smem(v, piece, p.out_dtype);
+          } else if (p.d != nullptr && row_ok) {
+            epi::store_chunk<CH>(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
+          }
+          if (red_any) {
+            if (p.red_axis == FUSEML_AXIS_M) {
+              // column reductions transpose 32 x 32 blocks in registers: 32-column chunks only (the
+              // host never picks the 16-warp instance for them)
+              if constexpr (CH == 32) {
+                float vs[CH], vm[CH];
+  #pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                  vs[i] = row_ok ? v[i] : 0.0f;
+                  vm[i] = row_ok ? v[i] : -INFINITY;
+                }
+                if (red_sum) colred[(quarter * 2 + 0) * BN + c * CH + lane] = warp_column_reduce<false>(vs, lane);
+                if (red_max) colred[(quarter * 2 + 1) * BN + c * CH + lane] = warp_column_reduce<true>(vm, lane);
               }
-              if (red_sum) colred[(quarter * 2 + 0) * BN + c * CH + lane] = warp_column_reduce<false>(vs, lane);
-              if (red_max) colred[(quarter * 2 + 1) * BN + c * CH + lane] = warp_column_reduce<true>(vm, lane);
+            } else if (n0 + CH <= p.N) {
+              // full chunk: pairwise packed adds (two chains), maxima as a tree
+              epi::f32x2 s0 = epi::pack2(v[0], v[1]), s1 = epi::pack2(v[2], v[3]);
+              float m0 = fmaxf(v[0], v[1]), m1 = fmaxf(v[2], v[3]);
+  #pragma unroll
+              for (int i = 4; i < CH; i += 4) {
+                s0 = epi::add2(s0, epi::pack2(v[i], v[i + 1]));
+                s1 = epi::add2(s1, epi::pack2(v[i + 2], v[i + 3]));
+                m0 = fmaxf(m0, fmaxf(v[i], v[i + 1]));
+                m1 = fmaxf(m1, fmaxf(v[i + 2], v[i + 3]));
+              }
+              float lo, hi;
+              epi::unpack2(epi::add2(s0, s1), lo, hi);
+              row_sum += lo + hi;
+              row_max = fmaxf(row_max, fmaxf(m0, m1));
+            } else {
+  #pragma unroll
+              for (int i = 0; i < CH; ++i) {
+                const bool in = (n0 + i < p.N);
+                row_sum += in ? v[i] : 0.0f;
+                row_max = in ? fmaxf(row_max, v[i]) : row_max;
+              }
             }
-          } else if (n0 + CH <= p.N) {
-            // full chunk: pairwise packed adds (two chains), maxima as a tree
-            epi::f32x2 s0 = epi::pack2(v[0], v[1]), s1 = epi::pack2(v[2], v[3]);
-            float m0 = fmaxf(v[0], v[1]), m1 = fmaxf(v[2], v[3]);
-#pragma unroll
-            for (int i = 4; i < CH; i += 4) {
-              s0 = epi::add2(s0, epi::pack2(v[i], v[i + 1]));
-              s1 = epi::add2(s1, epi::pack2(v[i + 2], v[i + 3]));
-              m0 = fmaxf(m0, fmaxf(v[i], v[i + 1]));
-              m1 = fmaxf(m1, fmaxf(v[i + 2], v[i + 3]));
-            }
-            float lo, hi;
-            epi::unpack2(epi::add2(s0, s1), lo, hi);
-            row_sum += lo + hi;
-            row_max = fmaxf(row_max, fmaxf(m0, m1));
-          } else {
-#pragma unroll
-            for (int i = 0; i < CH; ++i) {
-              const bool in = (n0 + i < p.N);
-              row_sum += in ? v[i] : 0.0f;
-              row_max = in ? fmaxf(row_max, v[i]) : row_max;
-            }
+          }
+      
+        }
+        if (EW == 16 && tile_out) {
+          ptx::fence_proxy_async_smem();
+          asm volatile("bar.sync 3, %0;" ::"n"(32 * EW) : "memory");
+          const int32_t box_n0 = n_tile0 + (c >> 2) * 64;
+          if (threadIdx.x == 64 && ok && box_n0 < p.N) {
+            ptx::tma_store_2d(&tmap_d, smem_base + (c >> 2) * kBoxBytes, box_n0, tm128 * kTileM);
+            ptx::bulk_commit_group();
           }
         }
       }
+      if (EW == 16 && tile_out && threadIdx.x == 64) ptx::bulk_wait_all();
       // accumulator drained: hand the TMEM buffer back to the (leader's) MMA thread
       ptx::tc_fence_before_sync();
       __syncwarp();

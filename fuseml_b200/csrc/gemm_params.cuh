@@ -50,6 +50,12 @@ struct GemmParams {
   // which is read by one or two tiles only: keeping it would push reusable data out of L2),
   // 2 = evict-last (the small operand everybody re-reads while the other one streams past)
   int32_t a_stream, b_stream;
+  // Tile I/O through shared memory (sixteen-warp instance, a CTA's only tile, tile width 256):
+  //   bit 0: the matrix operand (mat_slot) is brought in by TMA into the drained operand ring;
+  //   bit 1: the output tile is written to the ring and stored by TMA.
+  // Both replace row-per-thread global accesses (32 cache lines per warp-level instruction) by
+  // bulk copies of 128 x 64 boxes.
+  int32_t io_flags;
   int32_t* status;     // device status word (bounded-wait time-outs)
 };
 

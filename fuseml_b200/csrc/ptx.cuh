@@ -116,6 +116,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       : "memory");
 }
 
+// 2-D tiled store shared -> global (bulk async group).  The shared-memory box must have been
+// written through the generic proxy and published with fence_proxy_async_smem() before a
+// barrier that the issuing thread passes.  Out-of-range rows / columns are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src_smem, int32_t c0, int32_t c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(src_smem), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until every bulk group of this thread has completed (reads of shared memory and writes
+// to global memory)
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Same, with an L2 cache-policy hint (created by createpolicy).
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* tm, uint32_t bar,
                                                  int32_t c0, int32_t c1, uint64_t policy) {
