@@ -530,7 +530,7 @@ int fuseml_sm100_device_status(void* cuda_stream, int32_t* status_out) {
 // diagnostic builds only: copy the per-CTA stall counters of the last launches to the host
 int fuseml_debug_stalls(unsigned long long* out, int ctas) {
   if (ctas > 1024) ctas = 1024;
-  return cudaMemcpyFromSymbol(out, fuseml::v2::g_stall, sizeof(unsigned long long) * 12 * ctas) == cudaSuccess ? 0 : 1;
+  return cudaMemcpyFromSymbol(out, fuseml::v2::g_stall, sizeof(unsigned long long) * 16 * ctas) == cudaSuccess ? 0 : 1;
 }
 #endif
 

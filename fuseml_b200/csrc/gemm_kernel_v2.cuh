@@ -43,8 +43,9 @@ enum : int32_t {
 //   [6] wall clock (ns) at kernel entry                [7] wall clock (ns) just before the CTA exits
 //   [8] ... after set-up (barriers, TMEM, cluster sync) [9] ... when the MMA thread has issued everything
 //   [10] ... when epilogue warp 2 is done               [11] ... after the tear-down barriers
+//   [12..15] epilogue warp 2, cycles: TMEM load | epilogue program | store / tile write | final barrier + TMA store
 #ifdef FUSEML_STALL_COUNTERS
-__device__ unsigned long long g_stall[1024][12];
+__device__ unsigned long long g_stall[1024][16];
 #define FUSEML_STALL_T0() const long long stall_t0 = clock64()
 #define FUSEML_STALL_ADD(var) var += clock64() - stall_t0
 #else
@@ -432,6 +433,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     float all_sum = 0.0f, all_max = -INFINITY;
     bool ok = true;
     long long st_wait = 0, st_work = 0;
+#ifdef FUSEML_STALL_COUNTERS
+    long long st_ld = 0, st_prog = 0, st_store = 0, st_tail = 0;
+#endif
     for (int32_t t = unit; t < p.num_tiles; t += num_units) {
       int32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
@@ -549,17 +553,28 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           }
       
         }
-        if (EW == 16 && tile_out) {
-          ptx::fence_proxy_async_smem();
-          asm volatile("bar.sync 3, %0;" ::"n"(32 * EW) : "memory");
-          const int32_t box_n0 = n_tile0 + (c >> 2) * 64;
-          if (threadIdx.x == 64 && ok && box_n0 < p.N) {
-            ptx::tma_store_2d(&tmap_d, smem_base + (c >> 2) * kBoxBytes, box_n0, tm128 * kTileM);
-            ptx::bulk_commit_group();
+      }
+#ifdef FUSEML_STALL_COUNTERS
+      const long long c3 = clock64();
+#endif
+      if (EW == 16 && tile_out) {
+        // One barrier for the whole tile, not one per box: a barrier per 64 columns re-aligns
+        // the sixteen warps at every chunk, and warps in lock step queue up on the special-
+        // function unit instead of overlapping one warp's exp/rcp with another's FMAs.
+        ptx::fence_proxy_async_smem();
+        asm volatile("bar.sync 3, %0;" ::"n"(32 * EW) : "memory");
+        if (threadIdx.x == 64 && ok) {
+          for (int j = 0; j < 4; ++j) {
+            const int32_t box_n0 = n_tile0 + j * 64;
+            if (box_n0 < p.N) ptx::tma_store_2d(&tmap_d, smem_base + j * kBoxBytes, box_n0, tm128 * kTileM);
           }
+          ptx::bulk_commit_group();
+          ptx::bulk_wait_all();
         }
       }
-      if (EW == 16 && tile_out && threadIdx.x == 64) ptx::bulk_wait_all();
+#ifdef FUSEML_STALL_COUNTERS
+      st_tail += clock64() - c3;
+#endif
       // accumulator drained: hand the TMEM buffer back to the (leader's) MMA thread
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -607,6 +622,10 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       g_stall[blockIdx.x][3] = st_wait;
       g_stall[blockIdx.x][4] = st_work;
       g_stall[blockIdx.x][10] = ptx::globaltimer_ns();
+      g_stall[blockIdx.x][12] = st_ld;
+      g_stall[blockIdx.x][13] = st_prog;
+      g_stall[blockIdx.x][14] = st_store;
+      g_stall[blockIdx.x][15] = st_tail;
     }
 #else
     (void)st_wait; (void)st_work;
