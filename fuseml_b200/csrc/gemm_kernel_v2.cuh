@@ -501,25 +501,39 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
               ptx::prefetch_l1(mp + kEpiSplit * CH * 2 + 2 * CH - 1);
             }
           }
+#ifdef FUSEML_STALL_COUNTERS
+          const long long c0 = clock64();
+#endif
           uint32_t r[CH];
           ptx::tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(acc * BN + c * CH), r);
           ptx::tmem_ld_wait();
           float v[CH];
-  #pragma unroll
+#pragma unroll
           for (int i = 0; i < CH; ++i) v[i] = __uint_as_float(r[i]);
+#ifdef FUSEML_STALL_COUNTERS
+          const long long c1 = clock64();
+#endif
           epi::run_program<USES_SAVED, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
+#ifdef FUSEML_STALL_COUNTERS
+          const long long c2 = clock64();
+#endif
           if (tile_out) {
             if constexpr (CH == 16) epi::store_tile_smem(v, piece, p.out_dtype);
           } else if (p.d != nullptr && row_ok) {
             epi::store_chunk<CH>(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
           }
+#ifdef FUSEML_STALL_COUNTERS
+          st_ld += c1 - c0;
+          st_prog += c2 - c1;
+          st_store += clock64() - c2;
+#endif
           if (red_any) {
             if (p.red_axis == FUSEML_AXIS_M) {
               // column reductions transpose 32 x 32 blocks in registers: 32-column chunks only (the
               // host never picks the 16-warp instance for them)
               if constexpr (CH == 32) {
                 float vs[CH], vm[CH];
-  #pragma unroll
+#pragma unroll
                 for (int i = 0; i < CH; ++i) {
                   vs[i] = row_ok ? v[i] : 0.0f;
                   vm[i] = row_ok ? v[i] : -INFINITY;
@@ -531,7 +545,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
               // full chunk: pairwise packed adds (two chains), maxima as a tree
               epi::f32x2 s0 = epi::pack2(v[0], v[1]), s1 = epi::pack2(v[2], v[3]);
               float m0 = fmaxf(v[0], v[1]), m1 = fmaxf(v[2], v[3]);
-  #pragma unroll
+#pragma unroll
               for (int i = 4; i < CH; i += 4) {
                 s0 = epi::add2(s0, epi::pack2(v[i], v[i + 1]));
                 s1 = epi::add2(s1, epi::pack2(v[i + 2], v[i + 3]));
@@ -543,7 +557,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
               row_sum += lo + hi;
               row_max = fmaxf(row_max, fmaxf(m0, m1));
             } else {
-  #pragma unroll
+#pragma unroll
               for (int i = 0; i < CH; ++i) {
                 const bool in = (n0 + i < p.N);
                 row_sum += in ? v[i] : 0.0f;

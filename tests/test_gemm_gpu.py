@@ -374,3 +374,42 @@ def test_full_size_cfg3_reductions_match_unfused_path(K):
     e = torch.relu(case.tensors["A"][rows] @ case.tensors["B"])
     _assert_close(reds["max"][rows].cpu().numpy(), e.amax(-1).numpy(), "bf16", "amax vs eager")
     _assert_close(reds["mean"][rows].cpu().numpy(), e.double().mean(-1).float().numpy(), "bf16", "mean vs eager")
+
+
+@pytest.mark.parametrize("out_dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("M,Kd,Nn,pitch_pad", [(300, 256, 1000, 0), (256, 512, 2048, 0), (520, 192, 776, 8), (260, 128, 264, 3)])
+def test_lone_tile_path_is_bit_identical_to_the_persistent_path(K, M, Kd, Nn, pitch_pad, out_dtype):
+    """A launch whose CTA pairs get one tile each runs the sixteen-warp epilogue and moves the
+    residual and the output through shared memory by TMA; forcing two CTA pairs to walk all
+    tiles runs the eight-warp persistent path with direct loads and stores.  Same arithmetic in
+    the same order: the outputs must be equal bit for bit, ragged edges included.  A residual
+    whose row pitch is not a multiple of 16 bytes (pitch_pad = 3) cannot have a tensor map and
+    keeps the direct path in both."""
+    from fuseml_b200 import _native as N
+
+    g = torch.Generator().manual_seed(11)
+    td = {"bf16": torch.bfloat16, "f16": torch.float16}[out_dtype]
+    a = torch.randn(M, Kd, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(Nn, Kd, generator=g) / 8).to(torch.bfloat16).cuda()
+    bias = torch.randn(Nn, generator=g).to(torch.bfloat16).cuda()
+    r_full = torch.randn(M, Nn + pitch_pad, generator=g).to(torch.bfloat16).cuda()
+    resid = r_full[:, :Nn]
+    outs = []
+    for grid in (None, 4):
+        prog = K.EpilogueProgram().bias(bias).save().gelu().swap().sigmoid().mul_saved().add_tensor(resid)
+        out = torch.full((M, Nn), float("nan"), dtype=td, device="cuda")
+        desc = N.GemmDesc()
+        K.fill_desc(desc, a, w.t(), prog, out, td)
+        plan = K.plan_for(desc, K.device_props())
+        assert plan.cluster == 2 and plan.tile_n == 256
+        if grid is not None:
+            plan.grid = grid
+        K.fused_gemm(a, w.t(), prog, out_dtype=td, out=out, plan=plan)
+        torch.cuda.synchronize()
+        _status_ok(K)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    h = a.float() @ w.float().t() + bias.float()
+    ref = torch.nn.functional.gelu(h) * torch.sigmoid(h) + resid.float()
+    tol = BF16_TOL if out_dtype == "bf16" else dict(rtol=2e-3, atol=2e-3)
+    np.testing.assert_allclose(outs[0].float().cpu().numpy(), ref.cpu().numpy(), **tol)
