@@ -40,10 +40,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu captures summarised under profiles/gemm_epilogue_kernel_v2_*.md.  cfg4 is the
-# mean of its two launches (GEMM1 0.693 GB, GEMM2 1.959 GB: with K = 16384 the operand slabs of one
+# mean of its two launches (GEMM1 0.670 GB, GEMM2 1.751 GB: with K = 16384 the operand slabs of one
 # wave of tiles do not survive in L2 until the next wave; algorithmic bytes are 0.47 GB per launch).
 # cfg5 was not captured (same kernel as cfg4 at half the rows).
-NCU_TRAFFIC_BYTES = {"cfg4": 1.3263e9, "cfg2": 1.490e8, "cfg3": 1.485e8, "cfg5": None}
+NCU_TRAFFIC_BYTES = {"cfg4": 1.2108e9, "cfg2": 1.501e8, "cfg3": 1.508e8, "cfg5": None}
 
 
 def load_peaks():
