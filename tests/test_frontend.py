@@ -21,7 +21,8 @@ from fuseml_b200.codegen.kernel_generator import Sm100KernelGenerator, Unsupport
 from oracle import configs
 
 ROOT = Path(__file__).resolve().parent.parent
-REFERENCE = Path("/root/reference")
+# where a checkout of the reference may be found (its own pass-level tests are then run against this package)
+REFERENCE = Path(os.environ.get("FUSEML_REFERENCE_DIR", "/root/reference"))
 CFGS = list(configs.MAKERS)
 
 
