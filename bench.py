@@ -187,21 +187,32 @@ class MLPBlock(Workload):
     def step(self):
         return self._forward(self.x)
 
-    def e2e_step(self):
-        if not self.reductions:
-            # rows are independent: stream the batch through in row chunks, copy-in / kernels /
-            # copy-out on three CUDA streams (fuseml_b200.runtime), batches pipelining into each other
-            if self.runner is None:
-                from fuseml_b200.runtime import HostStreamedModule
+    def _forward_all(self, x):
+        """(y, sum, amax): what a caller of the stacked block gets back, scalars as 1-element tensors."""
+        y = self._forward(x)
+        s, m = self.scalars
+        return y, s.reshape(1), m.reshape(1)
 
-                # one chunk per batch measured best here: successive batches still pipeline into each other
-                self.runner = HostStreamedModule(self.compiled, rows_per_chunk=self.rows)
+    def e2e_step(self):
+        # rows are independent: copy-in / kernels / copy-out run on three CUDA streams
+        # (fuseml_b200.runtime), successive batches pipelining into each other; the metrics of the
+        # stacked workload travel back with the output, 4 bytes each, into pinned host memory
+        if self.runner is None:
+            from fuseml_b200.runtime import HostStreamedModule
+
+            # one chunk per batch measured best here: successive batches still pipeline into each other
+            self.runner = HostStreamedModule(self._forward_all if self.reductions else self.compiled,
+                                             rows_per_chunk=self.rows)
+            if self.reductions:
+                _, s, m = self._forward_all(self.x)
+                self.s_host = torch.empty(1, dtype=s.dtype).pin_memory()
+                self.m_host = torch.empty(1, dtype=m.dtype).pin_memory()
+                self.d2h_bytes = self.rows * self.D * 2 + s.element_size() + m.element_size()
+        if self.reductions:
+            self.runner.submit(self.x_host, (self.y_host, self.s_host, self.m_host))
+        else:
             self.runner.submit(self.x_host, self.y_host)
-            return None
-        self.x_in.copy_(self.x_host, non_blocking=True)
-        y = self._forward(self.x_in)
-        self.y_host.copy_(y, non_blocking=True)
-        return float(self.scalars[0]) + float(self.scalars[1])  # device->host read of the metrics
+        return None
 
     def e2e_finish(self):
         if self.runner is not None:

@@ -16,8 +16,9 @@ the stream-level runtime the B200 build adds around the same compiled callable.
     runner.synchronize()                   # y_pinned is complete
 
 ``submit`` may be called again before ``synchronize``: successive batches pipeline into
-each other.  Outputs may be one tensor or a tuple of tensors, each with the batch rows as
-its first dimension.
+each other.  Outputs may be one tensor or a tuple of tensors.  An output whose first
+dimension is the batch rows is copied out chunk by chunk; any other output (a scalar metric
+such as a global sum) is copied whole, which is only meaningful when the batch is one chunk.
 """
 from __future__ import annotations
 
@@ -120,7 +121,12 @@ class HostStreamedModule:
                 self._d2h.wait_event(done)
                 for t, o in zip(res_list, outs):
                     t.record_stream(self._d2h)                # allocated on the compute stream, read here
-                    o[r0:r1].copy_(t, non_blocking=True)
+                    if t.dim() > 0 and t.shape[0] == r1 - r0 and o.dim() == t.dim() and o.shape[0] == rows:
+                        o[r0:r1].copy_(t, non_blocking=True)
+                    elif rows <= self.rows_per_chunk:
+                        o.copy_(t.reshape(o.shape), non_blocking=True)   # a per-batch value (metric)
+                    else:
+                        raise ValueError("an output that does not follow the batch rows needs the batch in one chunk")
                     self.d2h_bytes += t.numel() * t.element_size()
             self.h2d_bytes += buf.numel() * buf.element_size()
 

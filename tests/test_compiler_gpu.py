@@ -125,6 +125,20 @@ def test_host_streamed_runtime_matches_direct_call(native_lib):
     assert runner.h2d_bytes == 3 * rows * d * 2 and runner.d2h_bytes == 3 * rows * d * 2
     with pytest.raises(ValueError):
         runner.submit(torch.zeros(4, d, dtype=torch.bfloat16), y_host)     # not pinned
+    # a per-batch metric next to the row output: copied whole when the batch is one chunk,
+    # refused when the batch is cut (it would be the metric of the last chunk only)
+    def with_metric(x):
+        y = compiled(x)
+        return y, y.float().sum().reshape(1)
+    s_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    whole = HostStreamedModule(with_metric, rows_per_chunk=rows)
+    whole.submit(x_host, (y_host, s_host))
+    whole.synchronize()
+    assert torch.equal(y_host, ref)
+    np.testing.assert_allclose(float(s_host), float(ref.float().sum()), rtol=1e-5)
+    with pytest.raises(ValueError):
+        HostStreamedModule(with_metric, rows_per_chunk=256).submit(x_host, (y_host, s_host))
+    torch.cuda.synchronize()
     torch._dynamo.reset()
 
 
