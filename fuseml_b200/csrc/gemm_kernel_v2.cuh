@@ -3,8 +3,11 @@
 //   warp 0      TMA producer: A and B tiles -> 128B-swizzled shared-memory ring
 //   warp 1      allocates TMEM; one thread (of the pair's leader CTA) issues tcgen05.mma with
 //               the fp32 accumulator in TMEM and frees ring stages with tcgen05.commit
-//   warps 2..9  epilogue: two warps per TMEM lane quarter, alternating 32-column chunks:
-//               tcgen05.ld, epilogue program in registers, 16-byte stores / reductions
+//   warps 2..   epilogue (EW = 8 warps: two per TMEM lane quarter on alternating 32-column
+//               chunks; EW = 16: four per quarter on 16-column chunks): tcgen05.ld, epilogue
+//               program in registers, 16-byte stores / reductions.  In launches where no CTA
+//               gets a second tile (EW = 16) the residual and output tiles move by TMA through
+//               the drained operand ring instead of row-per-thread global accesses.
 //
 // CG = 1: the CTA computes a 128 x BN tile.  CG = 2 (cluster of two CTAs, cta_group::2): the
 // pair computes 256 x BN; each CTA loads its own 128 rows of A and its own BN/2 columns of B,
@@ -565,7 +568,6 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
               }
             }
           }
-      
         }
       }
 #ifdef FUSEML_STALL_COUNTERS
