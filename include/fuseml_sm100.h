@@ -208,7 +208,11 @@ int fuseml_sm100_validate(const fuseml_gemm_desc_t* desc);
  * finalize kernel when a reduction is requested).  `plan` may be null.
  * Replaces fused_kernel[grid](...) (fuseml/codegen/kernel_launcher.py:811-814),
  * aten._addmm_activation (fuseml/codegen/cublas_epilogue.py:613-616) and
- * addmm_bias_residual (fuseml/codegen/cublas_epilogue.py:396-557). */
+ * addmm_bias_residual (fuseml/codegen/cublas_epilogue.py:396-557).
+ * Stream order: the kernel is launched with programmatic stream serialization and
+ * waits on the device for everything enqueued before it on `cuda_stream` before its
+ * first global access, so callers order work exactly as for an ordinary launch.
+ * The call never allocates, frees or synchronises; work is enqueued only. */
 int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan,
                                void* cuda_stream);
 
