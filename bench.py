@@ -502,6 +502,11 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------------------
 
+# config.workload of each --workload choice (the same string in both arms)
+WORKLOAD_NAMES = {"cfg1": "cfg1_fp32_mlp_small", "cfg2": "cfg2_act_heavy_gemm", "cfg3": "cfg3_gemm_row_reductions",
+                  "cfg4": "cfg4_mlp_block", "cfg5": "cfg5_stacked_mlp_x4"}
+
+
 def run_reference(args):
     """The reference arm: its CPU path for this workload on the host cores (rank 0 only)."""
     rank = int(os.environ.get("RANK", "0"))
@@ -514,7 +519,7 @@ def run_reference(args):
         "impl": "reference", "metric": "mlp_block_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": n, "warmup": 1, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "note": "CPU path of the reference = eager fp32 module (its compiler returns gm.forward on a CPU)"},
+        "config": {"workload": WORKLOAD_NAMES[args.workload], "note": "CPU path of the reference = eager fp32 module (its compiler returns gm.forward on a CPU)"},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
