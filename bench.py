@@ -14,8 +14,8 @@ N(0,1) activations, nn.Linear-initialised weights) and prints ONE JSON line with
                  timed on this machine's host cores on a bounded sample.
 
 ``--impl reference`` times that CPU path alone (rank 0 only).  ``--workload`` selects
-the other benchmark configurations (cfg2 weight-streaming GEMM, cfg3 GEMM + row
-reductions, cfg5 stacked MLP with global reductions).
+the other benchmark configurations (cfg1 small fp32 MLP, cfg2 weight-streaming GEMM,
+cfg3 GEMM + row reductions, cfg5 stacked MLP with global reductions).
 """
 from __future__ import annotations
 
