@@ -248,3 +248,20 @@ def test_batched_activations_fuse_through_the_flatten_views():
     ShapeProp(gm2).propagate(*args)
     (g2,) = F.FuseMLFusionPass(gm2)._find_fusion_groups()
     assert [s for s in g2.op_signature if "view" not in s] == ["aten.mm.default", "aten.relu.default"]
+
+
+def test_row_grouping_helpers():
+    """How reduction dims and outside operands line up with the flattened [rows, N] tile."""
+    from fuseml_b200.passes.topology import classify_epilogue_operand as c, reduction_axis_code as r
+
+    assert [r([-1], 3), r([2], 3), r(-1, 2), r([1], 2)] == ["n"] * 4
+    assert r([0], 2) == "m" and r([0], 3) is None and r([1], 3) is None
+    assert [r([], 3), r(None, 2), r([0, 1], 2), r([0, 1, 2], 3)] == ["all"] * 4
+    rows, n = 4 * 512, 256
+    assert c((4, 512, 256), rows, n) == "full" and c((2048, 256), rows, n) == "full"
+    assert c((256,), rows, n) == "row" and c((1, 1, 256), rows, n) == "row" and c((1, 256), rows, n) == "row"
+    assert c((4, 512, 1), rows, n) == "col" and c((2048, 1), rows, n) == "col" and c((2048,), rows, n) == "col"
+    assert c((), rows, n) == "scalar" and c((1, 1), rows, n) == "scalar"
+    assert c((512, 256), rows, n) is None            # broadcast over the batch only: not a [rows, N] pattern
+    assert c((4, 1, 256), rows, n) is None
+    assert c((256,), 256, 256) == "row"              # the reference's 1-D rule: length N runs along N first
