@@ -73,6 +73,7 @@ class Plan(C.Structure):
         ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32),
         ("cluster", C.c_int32), ("acc_stages", C.c_int32), ("grid", C.c_int32), ("group_m", C.c_int32),
         ("smem_bytes", C.c_int32), ("tmem_cols", C.c_int32), ("bound", C.c_int32), ("fuse", C.c_int32),
+        ("split_k", C.c_int32), ("reserved0", C.c_int32),
         ("flops", C.c_double), ("bytes", C.c_double), ("t_tensor_us", C.c_double),
         ("t_hbm_us", C.c_double), ("t_est_us", C.c_double),
     ]
@@ -157,7 +158,7 @@ def load(path: os.PathLike | str | None = None) -> C.CDLL:
         if missing:
             raise NativeLibraryError(f"{p} lacks symbols {missing}")
         _declare(lib)
-        if lib.fuseml_sm100_abi_version() != 1:
+        if lib.fuseml_sm100_abi_version() != 2:
             raise NativeLibraryError("ABI version mismatch between the Python binding and the library")
         if path is None:
             _lib = lib

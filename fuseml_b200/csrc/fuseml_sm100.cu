@@ -12,6 +12,7 @@
 #include "../../include/fuseml_sm100.h"
 #include "aux_kernels.cuh"
 #include "gemm_kernel_v2.cuh"
+#include "splitk_finish.cuh"
 #include "host_plan.h"
 
 namespace fuseml {
@@ -137,6 +138,8 @@ static int check_plan(const fuseml_plan_t* pl) {
   if (pl->grid <= 0 || pl->group_m <= 0) return FUSEML_E_PLAN;
   if (pl->cluster != 1 && pl->cluster != 2) return FUSEML_E_PLAN;
   if (pl->cluster == 2 && pl->tile_n <= 128) return FUSEML_E_PLAN;
+  if (pl->split_k < 0 || pl->split_k > 64 || pl->reserved0 != 0) return FUSEML_E_PLAN;
+  if (pl->split_k > 1 && pl->cluster != 1) return FUSEML_E_PLAN;
   return FUSEML_OK;
 }
 
@@ -230,6 +233,9 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   }
   rc = check_plan(&plan);
   if (rc != FUSEML_OK) return rc;
+  if (plan.split_k < 1) plan.split_k = 1;     // a zero-initialised plan means "no split"
+  // split-K has no fused reductions and needs an output to write
+  if (plan.split_k > 1 && (desc->reduce.kinds != 0 || desc->d == nullptr)) return FUSEML_E_PLAN;
 
   WorkspaceLayout w;
   workspace_layout(desc, &plan, &w);
@@ -340,6 +346,39 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   void* status_ptr = nullptr;
   if (cudaGetSymbolAddress(&status_ptr, g_status_word) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
   p.status = reinterpret_cast<int32_t*>(status_ptr);
+
+  if (plan.split_k > 1) {
+    // Split-K: every CTA runs one K slice of one tile and stores its raw fp32 accumulator; the
+    // epilogue program runs in splitk_finish_kernel on the folded slices.
+    const int32_t per = (p.num_kb + plan.split_k - 1) / plan.split_k;
+    const int32_t slices = (p.num_kb + per - 1) / per;          // none of them empty
+    GemmParams pg = p;
+    pg.split_k = slices;
+    pg.kb_per_split = per;
+    pg.split_ws = reinterpret_cast<float*>(ws + w.splitk_off);
+    pg.n_ops = 0;
+    pg.uses_saved = 0;
+    pg.vec_slot[0] = pg.vec_slot[1] = -1;
+    pg.mat_slot = -1;
+    CUtensorMap none;
+    std::memset(&none, 0, sizeof(none));
+    const int items = p.num_tiles * slices;
+    if (slices > 1) {
+      if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, none, none, pg, fmt, b_mn, items, stream);
+      else rc = launch_bn<128, 6, 1>(ta, tb, none, none, pg, fmt, b_mn, items, stream);
+      if (rc != FUSEML_OK) return rc;
+      GemmParams pf = p;
+      pf.split_k = slices;
+      pf.kb_per_split = per;
+      pf.split_ws = pg.split_ws;
+      for (int i = 0; i < pf.n_ops; ++i) pf.ops[i].reserved = 0;   // operands come straight from global memory
+      const int64_t work = desc->M * ((desc->N + kFinishChunk - 1) / kFinishChunk);
+      const int blocks = static_cast<int>((work + 255) / 256);
+      if (pf.uses_saved) splitk_finish_kernel<true><<<blocks, 256, 0, stream>>>(pf);
+      else splitk_finish_kernel<false><<<blocks, 256, 0, stream>>>(pf);
+      return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+    }
+  }
 
   int grid = std::min(plan.grid, p.num_tiles * CGr);
   if (desc->reduce.kinds != 0 && desc->reduce.axis == FUSEML_AXIS_ALL) {
@@ -492,7 +531,8 @@ int fuseml_sm100_gemm_epilogue_noalloc(const fuseml_gemm_desc_t* desc, const fus
   } else {
     fuseml_device_props_t props;
     if (fuseml_sm100_query(&props) != FUSEML_OK) return FUSEML_E_DEVICE;
-    rc = make_plan(desc, &props, &plan);
+    // a plan made here never splits K: the partial tiles would eat the fixed scratch budget
+    rc = make_plan(desc, &props, &plan, /*allow_split_k=*/false);
     if (rc != FUSEML_OK) return rc;
   }
   WorkspaceLayout w;

@@ -223,6 +223,14 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   if (threadIdx.x == 32) g_stall[blockIdx.x][8] = ptx::globaltimer_ns();
 #endif
   const int32_t num_kb = p.num_kb;
+  // Split-K launches give every CTA exactly one work item (tile, K slice); otherwise a tile
+  // walker strides over the tiles and owns their whole K loop.
+  const bool splitk = p.split_k > 1;
+  const int32_t k_slice = splitk ? unit / p.num_tiles : 0;
+  const int32_t first_tile = splitk ? unit % p.num_tiles : unit;
+  const int32_t tile_step = splitk ? p.num_tiles : num_units;
+  const int32_t kb_begin = splitk ? k_slice * p.kb_per_split : 0;
+  const int32_t kb_end = splitk ? (kb_begin + p.kb_per_split < num_kb ? kb_begin + p.kb_per_split : num_kb) : num_kb;
   // The tile width is a run-time value (a multiple of 32, at most BN): the router may shave it
   // so that the number of tiles fits the number of CTA pairs without a ragged last wave.
   const int32_t bn = p.bn;
@@ -239,12 +247,12 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const uint64_t pol_stream = ptx::policy_evict_first();
       const uint64_t pol_keep = ptx::policy_evict_last();
       long long st_empty = 0;
-      for (int32_t t = unit; t < p.num_tiles && ok; t += num_units) {
+      for (int32_t t = first_tile; t < p.num_tiles && ok; t += tile_step) {
         int32_t tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
         const int32_t m0 = tm * (kTileM * CG) + static_cast<int32_t>(cta_rank) * kTileM;
         const int32_t n0 = tn * bn + static_cast<int32_t>(cta_rank) * bn_cta;
-        for (int32_t kb = 0; kb < num_kb; ++kb) {
+        for (int32_t kb = kb_begin; kb < kb_end; ++kb) {
           FUSEML_STALL_T0();
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWhereProducerEmpty)) {
             ok = false;
@@ -357,7 +365,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
       const long long st_begin = clock64();
 #endif
-      for (int32_t t = unit; t < p.num_tiles && ok; t += num_units) {
+      for (int32_t t = first_tile; t < p.num_tiles && ok; t += tile_step) {
         {
           FUSEML_STALL_T0();
           if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kWhereMmaTmemEmpty)) {
@@ -368,7 +376,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int32_t kb = 0; kb < num_kb; ++kb) {
+        for (int32_t kb = kb_begin; kb < kb_end; ++kb) {
           // `ready` carries the result of a probe issued just before the previous K block's MMAs:
           // the barrier's round trip overlaps their issue instead of preceding the next ones
           if (!ready) {
@@ -392,7 +400,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           constexpr uint32_t kBStep = B_MN ? ((UMMA_K * kSwizzleBytes) >> 4) : (32u >> 4);
 #pragma unroll
           for (int k = 0; k < kKSteps; ++k) {
-            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint32_t accumulate = (kb > kb_begin || k > 0) ? 1u : 0u;
             if (CG == 2) {
               if (FMT == 2) ptx::mma_tf32_ss_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
               else ptx::mma_f16_ss_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
@@ -439,7 +447,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
     long long st_ld = 0, st_prog = 0, st_store = 0, st_tail = 0;
 #endif
-    for (int32_t t = unit; t < p.num_tiles; t += num_units) {
+    // where the tile goes: the output, or (split-K) this K slice's fp32 partial tile
+    void* const d_out = splitk ? static_cast<void*>(p.split_ws + static_cast<int64_t>(k_slice) * p.M * p.N) : p.d;
+    const int64_t ld_out = splitk ? static_cast<int64_t>(p.N) : p.ldd;
+    const int32_t dt_out = splitk ? static_cast<int32_t>(FUSEML_F32) : p.out_dtype;
+    for (int32_t t = first_tile; t < p.num_tiles; t += tile_step) {
       int32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
       const int32_t tm128 = tm * CG + static_cast<int32_t>(cta_rank);   // index of this CTA's 128-row block
@@ -522,8 +534,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #endif
           if (tile_out) {
             if constexpr (CH == 16) epi::store_tile_smem(v, piece, p.out_dtype);
-          } else if (p.d != nullptr && row_ok) {
-            epi::store_chunk<CH>(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
+          } else if (d_out != nullptr && row_ok) {
+            epi::store_chunk<CH>(d_out, static_cast<int64_t>(m) * ld_out, n0, p.N, dt_out, v);
           }
 #ifdef FUSEML_STALL_COUNTERS
           st_ld += c1 - c0;

@@ -129,7 +129,8 @@ static double operand_bytes(const fuseml_gemm_desc_t* d) {
   return b;
 }
 
-int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in, fuseml_plan_t* plan) {
+int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in, fuseml_plan_t* plan,
+              bool allow_split_k) {
   if (d == nullptr || plan == nullptr) return FUSEML_E_NULL;
   std::memset(plan, 0, sizeof(*plan));
   const int v = validate_desc(d);
@@ -207,12 +208,37 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
     const int64_t width = std::min<int64_t>(256, std::max<int64_t>(32, round_up(per_sm, 32)));
     if (width < best_bn) best_bn = static_cast<int>(width);
   }
+  // Split-K.  One K block costs a CTA about 570 cycles whatever the tile width (each MMA reads
+  // its 128-row slice of A from shared memory), so a problem with one row of tiles and a long
+  // K loop is bound by ceil(K/64) x 570 cycles per CTA however many SMs idle beside it.  Then
+  // several CTAs share one full-width tile's K loop, each writes an fp32 partial tile to the
+  // workspace, and a second kernel folds the partials in a fixed order and runs the epilogue.
+  // Only without fused reductions, and only when the partial tiles (which cross L2 twice) are
+  // small against what the split saves: at least 8 K blocks per CTA must disappear.
+  plan->split_k = 1;
+  if (allow_split_k && plan->cluster == 1 && tiles_m == 1 && d->reduce.kinds == 0 && d->d != nullptr) {
+    const int64_t num_kb = k_pad / plan->tile_k;
+    const int64_t wide_tiles = (d->N + 255) / 256;
+    const int64_t max_split = std::min<int64_t>({props.sm_count / std::max<int64_t>(1, wide_tiles), num_kb / 4, 32});
+    // the K loop of one CTA against the time the operands need to arrive from HBM anyway
+    const double t_loop_us = static_cast<double>(num_kb) * 570.0 / 1900.0;
+    const double t_floor_us = std::max(plan->t_hbm_us, 2.0);
+    int64_t want = static_cast<int64_t>(std::ceil(t_loop_us / t_floor_us));
+    want = std::min(want, max_split);
+    if (want >= 2 && t_loop_us > 1.5 * t_floor_us && num_kb - num_kb / want >= 8) {
+      // equal slices of ceil(num_kb / want) K blocks; drop the slices that would come out empty
+      const int64_t per = (num_kb + want - 1) / want;
+      plan->split_k = static_cast<int32_t>((num_kb + per - 1) / per);
+      best_bn = d->N > 128 ? 256 : 128;
+    }
+  }
   plan->tile_n = best_bn;
   const int cg = plan->cluster;
   const int64_t tiles_n = (d->N + best_bn - 1) / best_bn;
   const int64_t tiles = tiles_m * tiles_n;
   const int64_t units = std::max(1, props.sm_count / cg);
   plan->grid = static_cast<int32_t>(std::min<int64_t>(tiles, units) * cg);
+  if (plan->split_k > 1) plan->grid = static_cast<int32_t>(tiles * plan->split_k);   // one (tile, K slice) per CTA
   // Rasterisation: tiles are walked in groups of group_m tile rows (all columns of one group
   // before the next group).  The group's rows of A stay in L2 while B streams past once per
   // group, so DRAM reads are about bytes(A) + ceil(tiles_m / group_m) * bytes(B): the taller the
@@ -279,6 +305,10 @@ void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, Wo
       w->red_max_off = off;
       off += align256(partials * len * 4);
     }
+  }
+  if (plan->split_k > 1) {
+    w->splitk_off = off;
+    off += align256(static_cast<int64_t>(plan->split_k) * d->M * d->N * 4);
   }
   w->total = off;
 }

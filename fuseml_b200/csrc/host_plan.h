@@ -10,7 +10,9 @@ namespace fuseml {
 int dtype_bytes(int32_t dt);
 void default_props(fuseml_device_props_t* p);
 int validate_desc(const fuseml_gemm_desc_t* d);
-int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props, fuseml_plan_t* plan);
+// `allow_split_k = false` keeps the workspace free of partial tiles (fixed-budget callers).
+int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props, fuseml_plan_t* plan,
+              bool allow_split_k = true);
 
 // How B sits in memory: 0 = K contiguous (nn.Linear weight view), 1 = N
 // contiguous (row-major [K,N]), -1 = neither can be described by a TMA map.
@@ -24,6 +26,7 @@ struct WorkspaceLayout {
   int64_t split_a_off, split_b_off;  // fp32 operands only
   int64_t red_sum_off, red_max_off;  // reduction partials
   int64_t partials, len;             // partial arrays are [partials][len]
+  int64_t splitk_off;                // split-K: fp32 partial tiles, [split_k][M][N]
   int64_t total;
 };
 void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, WorkspaceLayout* w);

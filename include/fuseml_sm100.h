@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define FUSEML_SM100_ABI_VERSION 1
+#define FUSEML_SM100_ABI_VERSION 2
 
 /* ---- status codes ------------------------------------------------------ */
 enum {
@@ -167,6 +167,10 @@ typedef struct {
   int32_t tmem_cols;     /* TMEM columns allocated per CTA                   */
   int32_t bound;         /* 0 = HBM-bound, 1 = tensor-bound, 2 = latency     */
   int32_t fuse;          /* 1 = run fused kernel, 0 = router declines        */
+  int32_t split_k;       /* CTAs sharing one tile's K loop (1 = no split);   */
+                         /* > 1: fp32 partial tiles in the workspace, folded */
+                         /* and run through the epilogue by a second kernel  */
+  int32_t reserved0;     /* keeps the doubles 8-byte aligned; must be 0      */
   double flops;          /* 2*M*N*K                                          */
   double bytes;          /* algorithmic HBM bytes                            */
   double t_tensor_us;    /* flops / tensor peak                              */

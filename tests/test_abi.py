@@ -27,7 +27,7 @@ def test_every_declared_symbol_is_exported(native_lib):
 
 
 def test_abi_version_and_strerror(native_lib):
-    assert native_lib.fuseml_sm100_abi_version() == 1
+    assert native_lib.fuseml_sm100_abi_version() == 2
     assert N.strerror(0) == "ok"
     for code in range(1, 13):
         assert N.strerror(code) and "unknown" not in N.strerror(code)
@@ -112,8 +112,14 @@ def test_plan_budgets_and_bounds(native_lib):
     assert rc == N.OK and p.bound == 0 and p.t_hbm_us > p.t_tensor_us
     # tiny problem: latency-bound, still fused (single tier: no bypass)
     rc, p = _plan(native_lib, _desc(128, 512, 2048))
-    # one row of tiles: narrowed to 32 columns so that 16 CTAs share the K loop instead of 2
-    assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.cluster == 1 and (p.tile_n, p.grid) == (32, 16)
+    # one row of tiles and 32 K blocks: full-width tiles whose K loop is split over 5 CTAs each
+    # (partials in the workspace); a short K loop is only narrowed (32 columns, one tile per CTA)
+    assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.cluster == 1
+    assert (p.tile_n, p.split_k, p.grid) == (256, 5, 10)
+    d = _desc(128, 512, 2048)
+    assert native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(p)) == 5 * 128 * 512 * 4
+    rc, p = _plan(native_lib, _desc(128, 512, 256))
+    assert rc == N.OK and (p.tile_n, p.split_k, p.grid) == (32, 1, 16)
 
 
 def test_plan_follows_device_props(native_lib):
@@ -147,7 +153,8 @@ def test_workspace_bytes(native_lib):
     assert w(C.byref(d), None) == 2 * 16 * 2 * 8192 * 4
     d32 = _desc(128, 2048, 512, ab=N.F32)
     ld = 3 * 512
-    assert w(C.byref(d32), None) == (128 * ld + 2048 * ld) * 4
+    # the two expanded operands, plus 8 K slices' worth of fp32 partial tiles (48 K blocks split 8 ways)
+    assert w(C.byref(d32), None) == (128 * ld + 2048 * ld) * 4 + 8 * 128 * 2048 * 4
 
 
 def test_struct_layout_matches_header():
@@ -155,7 +162,7 @@ def test_struct_layout_matches_header():
     assert C.sizeof(N.Operand) == 32
     assert C.sizeof(N.Reduce) == 48
     assert C.sizeof(N.GemmDesc) == 656
-    assert C.sizeof(N.Plan) == 88
+    assert C.sizeof(N.Plan) == 96
     assert C.sizeof(N.DeviceProps) == 40
 
 

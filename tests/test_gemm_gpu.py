@@ -413,3 +413,42 @@ def test_lone_tile_path_is_bit_identical_to_the_persistent_path(K, M, Kd, Nn, pi
     ref = torch.nn.functional.gelu(h) * torch.sigmoid(h) + resid.float()
     tol = BF16_TOL if out_dtype == "bf16" else dict(rtol=2e-3, atol=2e-3)
     np.testing.assert_allclose(outs[0].float().cpu().numpy(), ref.cpu().numpy(), **tol)
+
+
+@pytest.mark.parametrize("dtype,M,Kd,Nn", [("bf16", 128, 4096, 1024), ("bf16", 37, 2048, 520), ("f16", 64, 8192, 264),
+                                            ("f32", 128, 512, 2048), ("bf16", 16, 16384, 4096)])
+def test_split_k_matches_the_single_pass_launch(K, dtype, M, Kd, Nn):
+    """Small-M problems with a long K loop are planned as split-K: several CTAs share one tile's
+    K loop, store fp32 partial tiles, and a second kernel folds them and runs the epilogue
+    (here a diamond with a residual and a row vector).  The same descriptor run with
+    split_k = 1 walks the whole K loop per tile: same result up to the fp32 summation order."""
+    from fuseml_b200 import _native as N
+
+    g = torch.Generator().manual_seed(5)
+    td = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    a = torch.randn(M, Kd, generator=g).to(td).cuda()
+    w = (torch.randn(Nn, Kd, generator=g) / Kd ** 0.5).to(td).cuda()
+    bias = torch.randn(Nn, generator=g).to(td).cuda()
+    resid = torch.randn(M, Nn, generator=g).to(td).cuda()
+    outs = []
+    for split in (None, 1):
+        prog = K.EpilogueProgram().bias(bias).save().gelu().swap().sigmoid().mul_saved().add_tensor(resid)
+        out = torch.full((M, Nn), float("nan"), dtype=td, device="cuda")
+        desc = N.GemmDesc()
+        K.fill_desc(desc, a, w.t(), prog, out, td)
+        plan = K.plan_for(desc, K.device_props())
+        if split is None:
+            assert plan.split_k > 1 and plan.cluster == 1, plan.as_dict()
+        else:
+            plan.split_k = 1
+            plan.grid = (Nn + plan.tile_n - 1) // plan.tile_n
+        K.fused_gemm(a, w.t(), prog, out_dtype=td, out=out, plan=plan)
+        torch.cuda.synchronize()
+        _status_ok(K)
+        outs.append(out.float().cpu().numpy())
+    h = a.double() @ w.double().t() + bias.double()
+    ref = (torch.nn.functional.gelu(h) * torch.sigmoid(h) + resid.double()).cpu().numpy()
+    tol = {"bf16": BF16_TOL, "f16": dict(rtol=2e-3, atol=2e-3), "f32": dict(rtol=1e-3, atol=1e-3)}[dtype]
+    np.testing.assert_allclose(outs[0], ref, **tol)
+    np.testing.assert_allclose(outs[1], ref, **tol)
+    np.testing.assert_allclose(outs[0], outs[1], **tol)
