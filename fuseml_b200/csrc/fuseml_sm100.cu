@@ -374,6 +374,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
       for (int i = 0; i < pf.n_ops; ++i) pf.ops[i].reserved = 0;   // operands come straight from global memory
       const int64_t work = desc->M * ((desc->N + kFinishChunk - 1) / kFinishChunk);
       const int blocks = static_cast<int>((work + 255) / 256);
+      // an ordinary launch: as a programmatic dependent (scheduled early, waiting on the device)
+      // it measured 20-35 % slower at high slice counts
       if (pf.uses_saved) splitk_finish_kernel<true><<<blocks, 256, 0, stream>>>(pf);
       else splitk_finish_kernel<false><<<blocks, 256, 0, stream>>>(pf);
       return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;

@@ -112,12 +112,12 @@ def test_plan_budgets_and_bounds(native_lib):
     assert rc == N.OK and p.bound == 0 and p.t_hbm_us > p.t_tensor_us
     # tiny problem: latency-bound, still fused (single tier: no bypass)
     rc, p = _plan(native_lib, _desc(128, 512, 2048))
-    # one row of tiles and 32 K blocks: full-width tiles whose K loop is split over 5 CTAs each
+    # one row of tiles and 32 K blocks: full-width tiles whose K loop is split over 4 CTAs each
     # (partials in the workspace); a short K loop is only narrowed (32 columns, one tile per CTA)
     assert rc == N.OK and p.bound == 2 and p.fuse == 1 and p.cluster == 1
-    assert (p.tile_n, p.split_k, p.grid) == (256, 5, 10)
+    assert (p.tile_n, p.split_k, p.grid) == (256, 4, 8)
     d = _desc(128, 512, 2048)
-    assert native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(p)) == 5 * 128 * 512 * 4
+    assert native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(p)) == 4 * 128 * 512 * 4
     rc, p = _plan(native_lib, _desc(128, 512, 256))
     assert rc == N.OK and (p.tile_n, p.split_k, p.grid) == (32, 1, 16)
 
@@ -153,8 +153,8 @@ def test_workspace_bytes(native_lib):
     assert w(C.byref(d), None) == 2 * 16 * 2 * 8192 * 4
     d32 = _desc(128, 2048, 512, ab=N.F32)
     ld = 3 * 512
-    # the two expanded operands, plus 8 K slices' worth of fp32 partial tiles (48 K blocks split 8 ways)
-    assert w(C.byref(d32), None) == (128 * ld + 2048 * ld) * 4 + 8 * 128 * 2048 * 4
+    # the two expanded operands, plus 6 K slices' worth of fp32 partial tiles (48 K blocks, 8 per slice)
+    assert w(C.byref(d32), None) == (128 * ld + 2048 * ld) * 4 + 6 * 128 * 2048 * 4
 
 
 def test_struct_layout_matches_header():
