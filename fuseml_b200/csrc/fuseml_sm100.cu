@@ -372,7 +372,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
       pf.kb_per_split = per;
       pf.split_ws = pg.split_ws;
       for (int i = 0; i < pf.n_ops; ++i) pf.ops[i].reserved = 0;   // operands come straight from global memory
-      const int64_t work = desc->M * ((desc->N + kFinishChunk - 1) / kFinishChunk);
+      const int64_t work = static_cast<int64_t>(p.num_tiles) * kTileM * (BN / kFinishChunk);
       const int blocks = static_cast<int>((work + 255) / 256);
       // an ordinary launch: as a programmatic dependent (scheduled early, waiting on the device)
       // it measured 20-35 % slower at high slice counts

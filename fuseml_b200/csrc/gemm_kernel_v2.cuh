@@ -447,10 +447,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
     long long st_ld = 0, st_prog = 0, st_store = 0, st_tail = 0;
 #endif
-    // where the tile goes: the output, or (split-K) this K slice's fp32 partial tile
-    void* const d_out = splitk ? static_cast<void*>(p.split_ws + static_cast<int64_t>(k_slice) * p.M * p.N) : p.d;
-    const int64_t ld_out = splitk ? static_cast<int64_t>(p.N) : p.ldd;
-    const int32_t dt_out = splitk ? static_cast<int32_t>(FUSEML_F32) : p.out_dtype;
+    // Split-K: this K slice's raw fp32 accumulator goes to the workspace in a layout made for
+    // the two kernels that touch it, [slice][tile][32-column chunk][16-byte piece][row][4]: one
+    // warp-level store writes 32 consecutive 16-byte pieces (512 contiguous bytes) instead of
+    // 32 pieces in 32 different rows, and splitk_finish_kernel reads them back the same way.
+    float* const split_tile = splitk ? p.split_ws + static_cast<int64_t>(k_slice) * p.num_tiles * (kTileM * bn) : nullptr;
     for (int32_t t = first_tile; t < p.num_tiles; t += tile_step) {
       int32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
@@ -534,8 +535,14 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #endif
           if (tile_out) {
             if constexpr (CH == 16) epi::store_tile_smem(v, piece, p.out_dtype);
-          } else if (d_out != nullptr && row_ok) {
-            epi::store_chunk<CH>(d_out, static_cast<int64_t>(m) * ld_out, n0, p.N, dt_out, v);
+          } else if (splitk) {
+            float4* dst = reinterpret_cast<float4*>(split_tile + static_cast<int64_t>(t) * (kTileM * bn)) +
+                          static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
+#pragma unroll
+            for (int i = 0; i < CH / 4; ++i)
+              dst[i * kTileM] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else if (p.d != nullptr && row_ok) {
+            epi::store_chunk<CH>(p.d, static_cast<int64_t>(m) * p.ldd, n0, p.N, p.out_dtype, v);
           }
 #ifdef FUSEML_STALL_COUNTERS
           st_ld += c1 - c0;

@@ -58,7 +58,8 @@ struct GemmParams {
   int32_t io_flags;
   // Split-K: split_k > 1 CTAs share one tile's K loop; work item t = tile + num_tiles * slice,
   // slice s covers K blocks [s * kb_per_split, ...); each CTA stores its raw fp32 accumulator
-  // to split_ws[s][M][N] and splitk_finish_kernel folds the slices and runs the epilogue.
+  // to split_ws[s][tile][column / 4][row][4] and splitk_finish_kernel folds the slices and runs
+  // the epilogue.
   int32_t split_k;
   int32_t kb_per_split;
   float* split_ws;

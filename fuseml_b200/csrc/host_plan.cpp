@@ -310,7 +310,10 @@ void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, Wo
   }
   if (plan->split_k > 1) {
     w->splitk_off = off;
-    off += align256(static_cast<int64_t>(plan->split_k) * d->M * d->N * 4);
+    // whole tiles (rows padded to 128, columns to the tile width): the kernels address them
+    // piece-major, see splitk_finish.cuh
+    const int64_t tiles = ((d->M + 127) / 128) * ((d->N + plan->tile_n - 1) / plan->tile_n);
+    off += align256(static_cast<int64_t>(plan->split_k) * tiles * 128 * plan->tile_n * 4);
   }
   w->total = off;
 }

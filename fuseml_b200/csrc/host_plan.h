@@ -26,7 +26,7 @@ struct WorkspaceLayout {
   int64_t split_a_off, split_b_off;  // fp32 operands only
   int64_t red_sum_off, red_max_off;  // reduction partials
   int64_t partials, len;             // partial arrays are [partials][len]
-  int64_t splitk_off;                // split-K: fp32 partial tiles, [split_k][M][N]
+  int64_t splitk_off;                // split-K: fp32 partial tiles, [split_k][tiles][128 x tile_n]
   int64_t total;
 };
 void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, WorkspaceLayout* w);

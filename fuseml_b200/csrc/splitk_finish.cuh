@@ -1,8 +1,7 @@
 // Second kernel of a split-K launch: folds the K slices' fp32 partial tiles in a fixed order
 // (slice 0, 1, 2, ...: the result does not depend on which CTA finished first), runs the
 // epilogue program on the sum and stores the output.  One thread per output row and 16
-// columns; neighbouring threads take neighbouring chunks of the same row, so the partials are
-// read and the output is written in contiguous 64-byte / 32-byte pieces.
+// columns.
 //
 // The reference has no counterpart (its Triton template always walks the whole K loop in one
 // program, fuseml/codegen/kernel_generator.py:1454-1542).
@@ -15,37 +14,40 @@ namespace fuseml {
 
 constexpr int kFinishChunk = 16;
 
+// Partial tiles are stored as [slice][tile][16-byte piece = column / 4][row][4 floats] (see the
+// GEMM kernel): a thread takes one row and four consecutive pieces (16 columns); threads that
+// are neighbours in a warp take neighbouring rows, so every load instruction of a warp reads
+// 512 contiguous bytes.
 template <bool USES_SAVED>
 __global__ void __launch_bounds__(256) splitk_finish_kernel(const __grid_constant__ GemmParams p) {
-  const int64_t chunks_per_row = (p.N + kFinishChunk - 1) / kFinishChunk;
+  const int32_t groups_per_tile = p.bn / kFinishChunk;               // 16-column groups in a tile
   const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-  if (idx >= chunks_per_row * p.M) return;
-  const int64_t m = idx / chunks_per_row;
-  const int32_t n0 = static_cast<int32_t>(idx - m * chunks_per_row) * kFinishChunk;
-  const int64_t slice = static_cast<int64_t>(p.M) * p.N;
-  const float* src = p.split_ws + m * p.N + n0;
+  const int32_t row = static_cast<int32_t>(idx % kTileM);
+  const int64_t rest = idx / kTileM;
+  const int32_t group = static_cast<int32_t>(rest % groups_per_tile);
+  const int64_t tile = rest / groups_per_tile;
+  if (tile >= p.num_tiles) return;
+  int32_t tm, tn;
+  tile_coords(static_cast<int32_t>(tile), p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
+  const int64_t m = static_cast<int64_t>(tm) * kTileM + row;
+  const int32_t n0 = tn * p.bn + group * kFinishChunk;
+  if (m >= p.M || n0 >= p.N) return;
+  const int64_t tile_floats = static_cast<int64_t>(kTileM) * p.bn;
+  const int64_t slice_floats = static_cast<int64_t>(p.num_tiles) * tile_floats;
+  const float4* src = reinterpret_cast<const float4*>(p.split_ws + tile * tile_floats) +
+                      static_cast<int64_t>(group) * (kFinishChunk / 4) * kTileM + row;
   float v[kFinishChunk];
 #pragma unroll
   for (int i = 0; i < kFinishChunk; ++i) v[i] = 0.0f;
-  const bool full = (n0 + kFinishChunk <= p.N);
-  if (full && (reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (slice & 3) == 0) {
-    for (int s = 0; s < p.split_k; ++s) {
-      const float4* q = reinterpret_cast<const float4*>(src + s * slice);
+  for (int s = 0; s < p.split_k; ++s) {
+    const float4* q = src + s * (slice_floats / 4);
 #pragma unroll
-      for (int i = 0; i < kFinishChunk / 4; ++i) {
-        const float4 x = __ldcs(q + i);   // read once: do not keep the partials in cache
-        v[4 * i + 0] += x.x;
-        v[4 * i + 1] += x.y;
-        v[4 * i + 2] += x.z;
-        v[4 * i + 3] += x.w;
-      }
-    }
-  } else {
-    for (int s = 0; s < p.split_k; ++s) {
-#pragma unroll
-      for (int i = 0; i < kFinishChunk; ++i) {
-        if (n0 + i < p.N) v[i] += src[s * slice + i];
-      }
+    for (int i = 0; i < kFinishChunk / 4; ++i) {
+      const float4 x = __ldcs(q + i * kTileM);   // read once: do not keep the partials in cache
+      v[4 * i + 0] += x.x;
+      v[4 * i + 1] += x.y;
+      v[4 * i + 2] += x.z;
+      v[4 * i + 3] += x.w;
     }
   }
   epi::run_program<USES_SAVED, kFinishChunk>(p, m, n0, true, v, nullptr, 0);
