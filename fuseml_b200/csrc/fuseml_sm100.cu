@@ -397,7 +397,10 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   CUtensorMap tr, td;
   std::memset(&tr, 0, sizeof(tr));
   std::memset(&td, 0, sizeof(td));
-  if (CGr == 2 && lone_tile && BN == 256) {
+  // tile I/O needs whole 64-column boxes; the sixteen-warp instances exist for the full-width
+  // pair kernel and for both single-CTA kernels
+  const bool staged = lone_tile && BN % 64 == 0 && (CGr == 1 || BN == 256);
+  if (staged) {
     // Tile I/O through shared memory: the matrix operand (residual) and the output tile move
     // as 128 x 64 boxes by TMA instead of row-per-thread accesses.  16-bit types, 16-byte
     // aligned base and row pitch (what a tensor map needs); anything else keeps the direct path.
@@ -410,7 +413,9 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
         encode_2d(&td, p.out_dtype, p.d, desc->M, desc->N, p.ldd, 64, kTileM) == FUSEML_OK) {
       p.io_flags |= 2;
     }
-    rc = launch_bn<256, 6, 2, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
+    if (CGr == 2) rc = launch_bn<256, 6, 2, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
+    else if (BN > 128) rc = launch_bn<256, 4, 1, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
+    else rc = launch_bn<128, 6, 1, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
   } else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
   else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
   else rc = launch_bn<128, 6, 1>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);

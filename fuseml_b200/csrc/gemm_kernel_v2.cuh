@@ -138,7 +138,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   constexpr int BN_CTA = BN / CG;                 // most B columns one CTA loads (sizes shared memory)
   constexpr uint32_t kTmemCols = 2 * BN;
   static_assert(EW == 8 || EW == 16, "two or four epilogue warps per TMEM lane quarter");
-  static_assert(EW == 8 || L::kStageBytes == 2 * kTileM * kSwizzleBytes, "tile I/O packs two boxes per ring stage");
+  static_assert(EW == 8 || L::kStageBytes % (kTileM * kSwizzleBytes) == 0, "tile I/O packs whole boxes into ring stages");
   constexpr int kEpiWarps = EW;
   constexpr int kEpiSplit = EW / 4;             // warps sharing one TMEM lane quarter
   constexpr int CH = (EW == 16) ? 16 : 32;      // accumulator columns per chunk
@@ -163,6 +163,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const bool tile_in = (EW == 16) && lone_tile && (p.io_flags & 1) != 0;
   const bool tile_out = (EW == 16) && lone_tile && (p.io_flags & 2) != 0;
   constexpr int kBoxBytes = kTileM * kSwizzleBytes;   // 128 rows x 64 16-bit columns
+  constexpr int kBoxesPerStage = L::kStageBytes / kBoxBytes;   // 2 (pairs, 128-wide) or 3 (256-wide single CTA)
+  const int32_t tile_boxes = p.bn / 64;               // boxes of this CTA's tile (tile I/O needs bn % 64 == 0)
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kBarOffset + L::kNumBars * 8);
   volatile uint32_t* abort_flag = tmem_base_slot + 1;
   float* colred = reinterpret_cast<float*>(smem + L::kRingBytes);
@@ -306,23 +308,21 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
       if (EW == 16 && tile_in && ok && unit < p.num_tiles) {
         // This CTA's only tile: as the last MMAs drain the ring, bring the tile of the matrix
-        // operand (residual) into the freed stages, boxes 0,1 -> stage 0, boxes 2,3 -> stage 1
-        // (a stage holds 32 KB, a box of 128 rows x 64 columns 16 KB).
+        // operand (residual) into the freed stages: a box of 128 rows x 64 columns is 16 KB, a
+        // stage holds two or three of them, the tile has bn / 64.
         int32_t tm, tn;
         tile_coords(unit, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
         const int32_t m0 = tm * (kTileM * CG) + static_cast<int32_t>(cta_rank) * kTileM;
         const int32_t n_tile0 = tn * bn;
-        ptx::mbar_arrive_expect_tx(tile_in_bar, 4 * kBoxBytes);
+        ptx::mbar_arrive_expect_tx(tile_in_bar, static_cast<uint32_t>(tile_boxes) * kBoxBytes);
         for (int i = 0; i < STAGES && ok; ++i) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, kWhereProducerEmpty)) {
             ok = false;
             break;
           }
-          if (stage < 2) {
-            const uint32_t dst = smem_base + stage * L::kStageBytes;
-            ptx::tma_load_2d(dst, &tmap_r, tile_in_bar, n_tile0 + stage * 128, m0);
-            ptx::tma_load_2d(dst + kBoxBytes, &tmap_r, tile_in_bar, n_tile0 + stage * 128 + 64, m0);
-          }
+          // the boxes that live in this stage's memory (box j sits at j * 16 KB from the ring base)
+          for (int j = stage * kBoxesPerStage; j < (stage + 1) * kBoxesPerStage && j < tile_boxes; ++j)
+            ptx::tma_load_2d(smem_base + j * kBoxBytes, &tmap_r, tile_in_bar, n_tile0 + j * 64, m0);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -599,7 +599,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         ptx::fence_proxy_async_smem();
         asm volatile("bar.sync 3, %0;" ::"n"(32 * EW) : "memory");
         if (threadIdx.x == 64 && ok) {
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < tile_boxes; ++j) {
             const int32_t box_n0 = n_tile0 + j * 64;
             if (box_n0 < p.N) ptx::tma_store_2d(&tmap_d, smem_base + j * kBoxBytes, box_n0, tm128 * kTileM);
           }

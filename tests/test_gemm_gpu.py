@@ -452,3 +452,35 @@ def test_split_k_matches_the_single_pass_launch(K, dtype, M, Kd, Nn):
     np.testing.assert_allclose(outs[0], ref, **tol)
     np.testing.assert_allclose(outs[1], ref, **tol)
     np.testing.assert_allclose(outs[0], outs[1], **tol)
+
+
+@pytest.mark.parametrize("M,Kd,Nn,tile_n", [(100, 256, 1000, 128), (128, 320, 1288, 256), (37, 128, 520, 64)])
+def test_single_cta_lone_tile_path_is_bit_identical_to_the_persistent_path(K, M, Kd, Nn, tile_n):
+    """The same comparison for one row of tiles (M <= 128, single-CTA kernels): one tile per CTA
+    runs the sixteen-warp instance with the residual and output tiles moved by TMA, two CTAs
+    walking all tiles run the eight-warp persistent path."""
+    from fuseml_b200 import _native as N
+
+    g = torch.Generator().manual_seed(13)
+    a = torch.randn(M, Kd, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(Nn, Kd, generator=g) / 8).to(torch.bfloat16).cuda()
+    bias = torch.randn(Nn, generator=g).to(torch.bfloat16).cuda()
+    resid = torch.randn(M, Nn, generator=g).to(torch.bfloat16).cuda()
+    tiles = (Nn + tile_n - 1) // tile_n
+    outs = []
+    for grid in (tiles, 2):
+        prog = K.EpilogueProgram().bias(bias).gelu().mul_tensor(resid).add_scalar(0.25)
+        out = torch.full((M, Nn), float("nan"), dtype=torch.bfloat16, device="cuda")
+        desc = N.GemmDesc()
+        K.fill_desc(desc, a, w.t(), prog, out, torch.bfloat16)
+        plan = K.plan_for(desc, K.device_props())
+        assert plan.cluster == 1
+        plan.tile_n, plan.split_k, plan.grid = tile_n, 1, grid
+        K.fused_gemm(a, w.t(), prog, out=out, plan=plan)
+        torch.cuda.synchronize()
+        _status_ok(K)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    h = a.float() @ w.float().t() + bias.float()
+    ref = torch.nn.functional.gelu(h) * resid.float() + 0.25
+    np.testing.assert_allclose(outs[0].float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
