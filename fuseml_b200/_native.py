@@ -14,6 +14,7 @@ from pathlib import Path
 
 MAX_EPI_OPS = 16
 MAX_OPERANDS = 8
+ABI_VERSION = 2          # FUSEML_SM100_ABI_VERSION of include/fuseml_sm100.h
 
 # status codes -----------------------------------------------------------------
 OK = 0
@@ -158,7 +159,7 @@ def load(path: os.PathLike | str | None = None) -> C.CDLL:
         if missing:
             raise NativeLibraryError(f"{p} lacks symbols {missing}")
         _declare(lib)
-        if lib.fuseml_sm100_abi_version() != 2:
+        if lib.fuseml_sm100_abi_version() != ABI_VERSION:
             raise NativeLibraryError("ABI version mismatch between the Python binding and the library")
         if path is None:
             _lib = lib

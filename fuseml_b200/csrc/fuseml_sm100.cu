@@ -61,36 +61,51 @@ static int encode_2d(CUtensorMap* tm, int32_t dtype, const void* base, int64_t r
   return r == CUDA_SUCCESS ? FUSEML_OK : FUSEML_E_LAYOUT;
 }
 
+constexpr int kMaxDevices = 64;
+
+// Per kernel instantiation and per device: the opt-in shared-memory attribute (sticky per
+// device function) and, for CTA pairs, how many clusters the device holds at once.  Looked up
+// once per device under a lock, so host threads driving different GPUs do not race; the
+// library has to be reloaded after cudaDeviceReset (the cached state describes the old context).
+struct InstanceState {
+  std::mutex mutex;
+  bool configured[kMaxDevices] = {false};
+  int max_clusters[kMaxDevices] = {0};
+};
+
 template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED, int CG, int EW>
 static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tr, const CUtensorMap& td,
                            const GemmParams& p, int grid, cudaStream_t stream) {
   using L = v2::Smem<BN, STAGES, CG>;
   auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, FMT, B_MN, SAVED, CG, EW>;
-  static int configured_device = -1;   // per instantiation; the attribute is sticky per device function
-  static int max_clusters = 0;
+  static InstanceState state;
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (configured_device != dev) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes) != cudaSuccess) {
-      cudaGetLastError();
-      return FUSEML_E_LAUNCH;
-    }
-    max_clusters = 0;
-    if (CG == 2) {
-      // how many CTA pairs the device can hold at once (GPCs with an odd SM count lose one SM)
-      cudaLaunchConfig_t q = {};
-      q.gridDim = dim3(2 * 148);
-      q.blockDim = dim3(v2::threads_for(EW));
-      q.dynamicSmemBytes = L::kDynamicBytes;
-      cudaLaunchAttribute qa[1];
-      qa[0].id = cudaLaunchAttributeClusterDimension;
-      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
-      q.attrs = qa; q.numAttrs = 1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return FUSEML_E_DEVICE; }
+  int max_clusters = 0;
+  {
+    std::lock_guard<std::mutex> lock(state.mutex);
+    if (!state.configured[dev]) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes) != cudaSuccess) {
+        cudaGetLastError();
+        return FUSEML_E_LAUNCH;
+      }
       int n = 0;
-      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 0; }
-      max_clusters = n;
+      if (CG == 2) {
+        // how many CTA pairs the device can hold at once (GPCs with an odd SM count lose one SM)
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(2 * 148);
+        q.blockDim = dim3(v2::threads_for(EW));
+        q.dynamicSmemBytes = L::kDynamicBytes;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+        q.attrs = qa; q.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 0; }
+      }
+      state.max_clusters[dev] = n;
+      state.configured[dev] = true;
     }
-    configured_device = dev;
+    max_clusters = state.max_clusters[dev];
   }
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
@@ -210,10 +225,14 @@ int64_t fuseml_sm100_workspace_bytes(const fuseml_gemm_desc_t* desc, const fusem
   fuseml_plan_t local;
   if (plan == nullptr) {
     if (make_plan(desc, nullptr, &local) != FUSEML_OK) return -1;
-    plan = &local;
+  } else {
+    // a caller's plan is checked before any arithmetic divides by its tile shape
+    if (validate_desc(desc) != FUSEML_OK || check_plan(plan) != FUSEML_OK) return -1;
+    local = *plan;
   }
+  if (local.split_k < 1) local.split_k = 1;
   WorkspaceLayout w;
-  workspace_layout(desc, plan, &w);
+  workspace_layout(desc, &local, &w);
   return w.total;
 }
 
@@ -500,7 +519,6 @@ namespace fuseml {
 constexpr int64_t kNoAllocScratchBytes = 8ll << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
-constexpr int kMaxDevices = 64;
 static void* g_noalloc_ptr[kMaxDevices] = {nullptr};
 static std::mutex g_noalloc_mutex;
 
@@ -542,6 +560,9 @@ int fuseml_sm100_gemm_epilogue_noalloc(const fuseml_gemm_desc_t* desc, const fus
     rc = make_plan(desc, &props, &plan, /*allow_split_k=*/false);
     if (rc != FUSEML_OK) return rc;
   }
+  rc = check_plan(&plan);
+  if (rc != FUSEML_OK) return rc;
+  if (plan.split_k < 1) plan.split_k = 1;
   WorkspaceLayout w;
   workspace_layout(desc, &plan, &w);
   if (w.total > kNoAllocScratchBytes) return FUSEML_E_LIMIT;

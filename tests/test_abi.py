@@ -157,6 +157,28 @@ def test_workspace_bytes(native_lib):
     assert w(C.byref(d32), None) == (128 * ld + 2048 * ld) * 4 + 6 * 128 * 2048 * 4
 
 
+def test_a_zeroed_or_garbage_plan_is_a_status_code_not_a_crash(native_lib):
+    """A caller's plan is checked before any arithmetic divides by its tile shape: a zeroed plan
+    with a reduction (or a split K loop) must come back as FUSEML_E_PLAN / -1."""
+    d = _desc(8192, 4096, 4096, kmajor=False)
+    d.reduce.kinds = N.RED_SUM
+    d.reduce.axis = N.AXIS_N
+    d.reduce.out_sum = 0x40000
+    zero = N.Plan()
+    assert native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(zero)) == -1
+    # both launch entries reject it on the host, before any CUDA call is made
+    assert native_lib.fuseml_sm100_gemm_epilogue(C.byref(d), C.byref(zero), None) == N.E_PLAN
+    assert native_lib.fuseml_sm100_gemm_epilogue_noalloc(C.byref(d), C.byref(zero), None) == N.E_PLAN
+    rc, good = _plan(native_lib, d)
+    assert rc == N.OK
+    for field, value in (("tile_n", 0), ("tile_n", 48), ("tile_m", 64), ("grid", 0), ("group_m", 0), ("cluster", 3),
+                         ("split_k", 65), ("reserved0", 1)):
+        bad = N.Plan.from_buffer_copy(good)
+        setattr(bad, field, value)
+        assert native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(bad)) == -1, field
+        assert native_lib.fuseml_sm100_gemm_epilogue_noalloc(C.byref(d), C.byref(bad), None) == N.E_PLAN, field
+
+
 def test_struct_layout_matches_header():
     assert C.sizeof(N.EpiOp) == 16
     assert C.sizeof(N.Operand) == 32

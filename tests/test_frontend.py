@@ -21,8 +21,9 @@ from fuseml_b200.codegen.kernel_generator import Sm100KernelGenerator, Unsupport
 from oracle import configs
 
 ROOT = Path(__file__).resolve().parent.parent
-# where a checkout of the reference may be found (its own pass-level tests are then run against this package)
-REFERENCE = Path(os.environ.get("FUSEML_REFERENCE_DIR", "/root/reference"))
+# FUSEML_REFERENCE_DIR names a checkout of the reference; its own pass-level tests are then run
+# against this package (skipped when the variable is unset)
+REFERENCE = Path(os.environ["FUSEML_REFERENCE_DIR"]) if os.environ.get("FUSEML_REFERENCE_DIR") else None
 CFGS = list(configs.MAKERS)
 
 
@@ -186,7 +187,8 @@ REF_TESTS = ["test_registry", "test_fusion_group", "test_pattern_matching", "tes
              "test_mutation_safety", "test_control_flow_validation", "test_end_to_end", "test_kernel_cache"]
 
 
-@pytest.mark.skipif(not (REFERENCE / "tests").is_dir(), reason="reference checkout not present on this machine")
+@pytest.mark.skipif(REFERENCE is None or not (REFERENCE / "tests").is_dir(),
+                    reason="FUSEML_REFERENCE_DIR does not name a reference checkout")
 def test_reference_pass_level_suite_passes_against_this_package(tmp_path):
     """Run the reference's own structural tests, unmodified and in place, with ``fuseml``
     resolving to this package."""
