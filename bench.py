@@ -1,30 +1,36 @@
 #!/usr/bin/env python
 """Benchmark of the fused GEMM + epilogue path on B200.
 
-``python bench.py --gpus N --steps K --warmup W`` runs the residual Transformer-MLP
-block (d_model 4096, d_intermediate 16384, 8192 tokens per GPU, bf16; synthetic
-N(0,1) activations, nn.Linear-initialised weights) and prints ONE JSON line with
+``python bench.py --gpus N --steps K --warmup W`` runs the residual Transformer-MLP block
+(d_model 4096, d_intermediate 16384, 8192 tokens, bf16; synthetic N(0,1) activations,
+nn.Linear-initialised weights), its rows sharded over the N GPUs (strong scaling, weights
+replicated, no collective), and prints ONE JSON line with
 
-* ``value``      tokens/s over all GPUs, inputs resident in HBM, CUDA-event timed;
-* ``e2e``        the same metric through the public call with pinned HOST buffers
-                 (host->device copy of the tokens and device->host read of the result
-                 inside the timed region);
-* ``roofline``   the dominant kernel's achieved TFLOP/s (or GB/s) against the measured peak;
-* ``cpu_baseline`` the CPU oracle (fp32 eager, what the reference executes on a CPU)
-                 timed on this machine's host cores on a bounded sample.
+* ``value``      tokens/s over all GPUs, inputs resident in HBM, K steps timed with CUDA events;
+* ``e2e``        the same metric through the public call with pinned HOST buffers (host->device
+                 copy of the tokens and device->host read of the result inside the timed region),
+                 next to the copy-only ceiling of the same buffers on the same streams;
+* ``roofline``   the dominant kernel's achieved TFLOP/s (or GB/s) over the K timed steps against
+                 the measured peak of the matching regime (burst for a region well under a
+                 second), and ``roofline_sustained``: the same step repeated for at least a
+                 second, against the sustained peak, clocks sampled inside that region only;
+* ``workloads``  the other benchmark configurations (cfg1 small fp32 MLP, cfg2 weight-streaming
+                 GEMM, cfg3 GEMM + row reductions, cfg5 stacked MLP with global reductions and,
+                 on several GPUs, its all-reduce), each timed for at least a second;
+* ``cpu_baseline`` the CPU oracle (fp32 eager, what the reference executes on a CPU) timed on this
+                 machine's host cores on a bounded sample.
 
-``--impl reference`` times that CPU path alone (rank 0 only).  ``--workload`` selects
-the other benchmark configurations (cfg1 small fp32 MLP, cfg2 weight-streaming GEMM,
-cfg3 GEMM + row reductions, cfg5 stacked MLP with global reductions).
+``--impl reference`` times that CPU path alone (rank 0 only).  ``--workload`` makes another
+configuration the headline; ``--no-extras`` skips the ``workloads`` sub-records.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
-import subprocess
 import sys
-import tempfile
+import threading
 import time
 from pathlib import Path
 
@@ -377,13 +383,9 @@ def make_workload(name, world, scaling):
     if name == "cfg1":
         return SmallFp32MLP()
     if name == "cfg4":
-        rows = 8192 if scaling == "weak" else 8192 // world
-        return MLPBlock(rows, world=world)
+        return MLPBlock(8192 if scaling == "weak" else 8192 // world, world=world)
     if name == "cfg5":
-        rows = 32768 // world if scaling == "strong" else 32768 // 8  # 4096 rows per GPU, as at 8 GPUs
-        if world == 1 and scaling == "strong":
-            rows = 32768
-        return MLPBlock(rows, blocks=4, reductions=True, world=world)
+        return MLPBlock(32768 if scaling == "weak" else 32768 // world, blocks=4, reductions=True, world=world)
     if name == "cfg2":
         return ActHeavyGemm()
     if name == "cfg3":
@@ -391,11 +393,37 @@ def make_workload(name, world, scaling):
     raise SystemExit(f"unknown workload {name}")
 
 
+# config.workload of each --workload choice (the same string in both arms)
+WORKLOAD_NAMES = {"cfg1": "cfg1_fp32_mlp_small", "cfg2": "cfg2_act_heavy_gemm", "cfg3": "cfg3_gemm_row_reductions",
+                  "cfg4": "cfg4_mlp_block", "cfg5": "cfg5_stacked_mlp_x4"}
+GLOBAL_ROWS = {"cfg1": 128, "cfg2": 256, "cfg3": 8192, "cfg4": 8192, "cfg5": 32768}
+SHARDED = ("cfg4", "cfg5")
+
+
+def workload_config(name, world, scaling):
+    """The ``config`` object of the JSON line: the same in both arms."""
+    sharded = name in SHARDED and world > 1
+    per_gpu = GLOBAL_ROWS[name] if (scaling == "weak" or not sharded) else GLOBAL_ROWS[name] // world
+    return {
+        "workload": WORKLOAD_NAMES[name], "rows_per_gpu": per_gpu,
+        "global_rows": per_gpu * world if name in SHARDED else per_gpu,
+        "l2": ("9 MB working set, resident in L2: a latency-bound parity configuration, not a roofline claim"
+               if name == "cfg1" else
+               "inputs larger than L2 (weights + activations per step exceed 126 MB"
+               + ("; weight copies rotated)" if name == "cfg2" else ")")),
+        "parallelism": (f"rows sharded over {world} GPU(s), weights replicated" if name in SHARDED
+                        else "one GPU per replica"),
+    }
+
+
 # --------------------------------------------------------------------------------------
 # CPU baseline: the oracle's eager fp32 module on the host cores
 # --------------------------------------------------------------------------------------
 
-def cpu_baseline(workload_name, budget_s=20.0, steps=None, sample_rows=None):
+CPU_SAMPLE_ROWS = {"cfg1": 128, "cfg4": 512, "cfg5": 128, "cfg3": 512, "cfg2": 64}
+
+
+def cpu_baseline(workload_name, budget_s=20.0, steps=None, warmup=1):
     """Times the CPU oracle (fp32 eager module = what the reference runs on a CPU) on a
     bounded sample of the workload.  Returns (tokens_per_s, description, cores, ms_per_step, steps)."""
     from oracle import configs
@@ -403,12 +431,12 @@ def cpu_baseline(workload_name, budget_s=20.0, steps=None, sample_rows=None):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     full = dict(configs.FULL[workload_name])
-    default_rows = {"cfg1": 128, "cfg4": 512, "cfg5": 128, "cfg3": 512, "cfg2": 64}[workload_name]
-    rows = sample_rows or default_rows
+    rows = CPU_SAMPLE_ROWS[workload_name]
     full["M"] = rows
     case = configs.make(workload_name, sizes=full)
     with torch.no_grad():
-        case.module(*case.args)  # warm-up
+        for _ in range(max(1, warmup)):
+            case.module(*case.args)
         times = []
         t_start = time.perf_counter()
         n = 0
@@ -422,109 +450,275 @@ def cpu_baseline(workload_name, budget_s=20.0, steps=None, sample_rows=None):
                     break
             elif time.perf_counter() - t_start > budget_s or n >= 50:
                 break
-    times.sort()
-    med = times[len(times) // 2]
+    mean = sum(times) / len(times)
     desc = (f"{workload_name} at full width, {rows} of the rows per step, fp32 eager PyTorch on "
-            f"{cores} threads, median of {n} steps")
-    return rows / med, desc, cores, med * 1e3, n
+            f"{cores} threads, mean of {n} steps after {max(1, warmup)} warm-up")
+    return rows / mean, desc, cores, mean * 1e3, n
 
 
 # --------------------------------------------------------------------------------------
-# clocks
+# clocks: NVML polled from a thread, only while a timed region runs
 # --------------------------------------------------------------------------------------
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """SM clock, power and clock-event reasons of one GPU, polled through NVML every few
+    milliseconds between ``start()`` and ``stop()``.  The host thread that launches the timed
+    steps spends the region inside ``cudaDeviceSynchronize`` (GIL released), so the poller runs."""
 
-    def __init__(self, gpu_index):
-        self.gpu = gpu_index
-        self.proc = None
-        self.path = None
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, cuda_index):
+        self.handle = None
+        self.nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            props = torch.cuda.get_device_properties(cuda_index)
+            bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+            self.handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            self.nvml = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.handle = None
+        self._stop = threading.Event()
+        self._thread = None
+        self.samples = []
+
+    def _poll(self):
+        nv, h = self.nvml, self.handle
+        while not self._stop.is_set():
+            try:
+                clk = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                watts = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                self.samples.append((clk, watts, mask))
+            except Exception:
+                pass
+            self._stop.wait(0.004)
 
     def start(self):
-        try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
-
-    def samples_so_far(self):
-        try:
-            return sum(1 for l in open(self.path) if l.strip())
-        except Exception:
-            return 0
-
-    def wait_for_samples(self, n, timeout_s=3.0):
-        """nvidia-smi takes a moment to start: block (bounded) until it has written n samples."""
-        t0 = time.perf_counter()
-        while self.proc is not None and self.samples_so_far() < n and time.perf_counter() - t0 < timeout_s:
-            time.sleep(0.02)
+        self.samples = []
+        self._stop.clear()
+        if self.handle is not None:
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        try:
-            self.proc.terminate()
-            self.proc.wait(timeout=5)
-        except Exception:
-            pass
-        try:
-            rows = [l.strip().split(", ") for l in open(self.path).read().strip().splitlines() if l.strip()]
-            os.unlink(self.path)
-        except Exception:
-            return out
-        samples, mx = [], None
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in rows:
-            if len(r) < 7:
-                continue
-            try:
-                clk, mx, watts = float(r[0]), float(r[1]), float(r[2])
-            except ValueError:
-                continue
-            samples.append((clk, watts, {nm for nm, v in zip(names, r[3:7]) if v.strip().lower() == "active"}))
-        if samples:
-            # "under load" = samples drawing at least half of the highest power seen in the window
-            p_max = max(w for _, w, _ in samples)
-            loaded = [x for x in samples if x[1] >= 0.5 * p_max] or samples
-            clks = sorted(c for c, _, _ in loaded)
-            reasons = set().union(*[rs for _, _, rs in loaded])
-            out.update(sm_mhz=clks[len(clks) // 2], sm_max_mhz=mx, reasons=sorted(reasons), samples=len(samples),
-                       samples_under_load=len(loaded), power_w_max=p_max)
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2.0)
+            self._thread = None
+        out = {"sm_mhz": None, "sm_max_mhz": getattr(self, "max_mhz", None), "reasons": [], "samples": len(self.samples),
+               "window": "inside the timed region only"}
+        if self.samples:
+            clks = sorted(c for c, _, _ in self.samples)
+            mask = 0
+            for _, _, m in self.samples:
+                mask |= m
+            out.update(sm_mhz=clks[len(clks) // 2], sm_mhz_min=clks[0], sm_mhz_max=clks[-1],
+                       reasons=sorted(n for b, n in self.REASONS.items() if mask & b),
+                       power_w_max=max(w for _, w, _ in self.samples))
         return out
 
 
 # --------------------------------------------------------------------------------------
-
-# config.workload of each --workload choice (the same string in both arms)
-WORKLOAD_NAMES = {"cfg1": "cfg1_fp32_mlp_small", "cfg2": "cfg2_act_heavy_gemm", "cfg3": "cfg3_gemm_row_reductions",
-                  "cfg4": "cfg4_mlp_block", "cfg5": "cfg5_stacked_mlp_x4"}
-
 
 def run_reference(args):
     """The reference arm: its CPU path for this workload on the host cores (rank 0 only)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, args.steps)
-    # warm-up passes are part of cpu_baseline(); `steps` timed passes over a bounded sample
-    val, desc, cores, ms, n = cpu_baseline(args.workload, steps=min(steps, 20))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    steps, warm = max(1, args.steps), max(1, args.warmup)
+    # the sample is sized so that `steps` + `warmup` passes end within a few minutes
+    val, desc, cores, ms, n = cpu_baseline(args.workload, steps=min(steps, 100), warmup=min(warm, 10))
     line = {
         "impl": "reference", "metric": "mlp_block_tokens_per_s", "value": val, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": n, "warmup": 1, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAMES[args.workload], "note": "CPU path of the reference = eager fp32 module (its compiler returns gm.forward on a CPU)"},
+        "n_gpus": args.gpus, "steps": n, "warmup": min(warm, 10), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, world, args.scaling),
+        "note": "CPU path of the reference = eager fp32 module (its compiler returns gm.forward on a CPU); "
+                "each step is a bounded row sample of the workload at full width",
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+class Harness:
+    """Timing on one rank of the job: barriers, CUDA events, max over ranks, clocks inside the region."""
+
+    def __init__(self, dist, sampler):
+        self.dist = dist
+        self.sampler = sampler
+
+    def barrier(self):
+        torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+        torch.cuda.synchronize()
+
+    def allmax(self, v):
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        if self.dist is not None:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, fn, n, finish=None, clocks=True):
+        """ms for n calls of fn (max over ranks) and the clock record of exactly that region."""
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if clocks and self.sampler is not None:
+            self.sampler.start()
+        e0.record()
+        for _ in range(n):
+            fn()
+        if finish is not None:
+            finish()          # make the timing stream wait for work enqueued on other streams
+        e1.record()
+        torch.cuda.synchronize()
+        rec = self.sampler.stop() if clocks and self.sampler is not None else {}
+        ms = self.allmax(e0.elapsed_time(e1))
+        self.barrier()
+        return ms, rec
+
+    def timed_for(self, fn, seconds, per_step_ms, finish=None):
+        """Repeat fn for at least `seconds`; the count comes from an all-reduced estimate, so every
+        rank runs the same number of steps (and collectives)."""
+        n = max(3, min(200000, int(math.ceil(seconds * 1e3 / max(per_step_ms, 1e-3)))))
+        ms, rec = self.timed(fn, n, finish=finish)
+        return ms, n, rec
+
+
+def roofline_of(wl, name, launch_ms, region_s, peaks, peak_src):
+    """Achieved rate of the dominant kernel over a timed region against the measured peak of the
+    regime the region ran in: a region well under a second is a burst (the GPU has not settled at
+    the power cap yet), a region of a second or more is sustained."""
+    if wl.bound == "tensor":
+        achieved = wl.flops_per_launch / (launch_ms * 1e-3) / 1e12
+        kind = "bf16_tflops" if region_s < 0.5 else "bf16_tflops_sustained"
+        peak = peaks[kind]
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_kind": f"{kind}, {peak_src}", "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
+                "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"]}
+    else:
+        achieved = wl.algo_bytes / (launch_ms * 1e-3) / 1e9
+        peak = peaks["hbm_gbs"]
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_kind": f"hbm_gbs, {peak_src}"}
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(name)
+    roof["kernel"] = "gemm_epilogue_kernel_v2"
+    roof["launch_us"] = launch_ms * 1e3
+    roof["region_s"] = region_s
+    return roof
+
+
+def prepare(wl, W, use_graph):
+    for _ in range(W):
+        wl.step()
+    wl.check_compiled()
+    graphed = False
+    if use_graph:
+        try:
+            graphed = wl.use_graphs()
+        except Exception as exc:          # capture is an optimisation, never a requirement
+            print(f"[bench] CUDA graph capture failed, stepping eagerly: {exc!r}", file=sys.stderr)
+            wl.graphs = None
+        for _ in range(3):
+            wl.step()
+    torch.cuda.synchronize()
+    return graphed
+
+
+def check_status():
+    from fuseml_b200 import kernels as K
+
+    status = K.device_status()
+    if status != 0:
+        raise SystemExit(f"device status {status:#x}: a bounded wait ran out; numbers would be meaningless")
+
+
+def link_ceiling(h, wl, steps):
+    """Copy-only ceiling of the end-to-end path: the same pinned buffers, one host->device and one
+    device->host copy per step on two streams, no kernel; every rank at once.  ms per step."""
+    ins = [t for t in (getattr(wl, n, None) for n in ("x_host", "r_host", "a_host")) if t is not None]
+    outs = [t for t in (getattr(wl, n, None) for n in ("y_host", "out_host")) if t is not None]
+    dev_in = [torch.empty_like(t, device="cuda") for t in ins]
+    dev_out = [torch.empty_like(t, device="cuda") for t in outs]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def copy_step():
+        with torch.cuda.stream(s_in):
+            for d, t in zip(dev_in, ins):
+                d.copy_(t, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for d, t in zip(dev_out, outs):
+                t.copy_(d, non_blocking=True)
+
+    def finish():
+        cur = torch.cuda.current_stream()
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
+
+    for _ in range(2):
+        copy_step()
+    finish()
+    ms, _ = h.timed(copy_step, steps, finish=finish, clocks=False)
+    return ms / steps
+
+
+def measure(h, wl, name, W, steps, use_graph, peaks, peak_src, world, sustained_s=1.0):
+    """K timed steps (the headline numbers) and the same step repeated for `sustained_s` seconds."""
+    graphed = prepare(wl, W, use_graph)
+    before = wl.fused_launches()
+    total_ms, clocks = h.timed(wl.step, steps)
+    launches = wl.gemm_launches_per_step * steps if graphed else wl.fused_launches() - before
+    launches += steps * (wl.launches_per_step - wl.gemm_launches_per_step)
+    check_status()
+    ms_per_step = total_ms / steps
+    out = {
+        "ms_per_step": ms_per_step, "steps": steps, "tokens_per_s": wl.tokens * world / (ms_per_step * 1e-3),
+        "tflops": wl.flops * world / (ms_per_step * 1e-3) / 1e12,
+        "roofline": roofline_of(wl, name, ms_per_step / wl.gemm_launches_per_step, total_ms * 1e-3, peaks, peak_src),
+        "clocks": clocks, "gpu_launches": launches, "cuda_graph": bool(graphed),
+    }
+    if sustained_s:
+        s_ms, n, s_clocks = h.timed_for(wl.step, sustained_s, ms_per_step)
+        check_status()
+        out["sustained"] = {
+            "ms_per_step": s_ms / n, "steps": n, "tokens_per_s": wl.tokens * world / (s_ms / n * 1e-3),
+            "roofline": roofline_of(wl, name, s_ms / n / wl.gemm_launches_per_step, s_ms * 1e-3, peaks, peak_src),
+            "clocks": s_clocks,
+        }
+    return out
+
+
+def measure_e2e(h, wl, steps, world):
+    ceiling_ms = link_ceiling(h, wl, steps)
+    for _ in range(2):
+        wl.e2e_step()
+    wl.e2e_finish()
+    e2e_ms, _ = h.timed(wl.e2e_step, steps, finish=wl.e2e_finish, clocks=False)
+    per = e2e_ms / steps
+    moved = (wl.h2d_bytes + wl.d2h_bytes) * world
+    return {"value": wl.tokens * world / (per * 1e-3), "unit": "tokens/s",
+            "h2d_bytes_per_step": wl.h2d_bytes * world, "d2h_bytes_per_step": wl.d2h_bytes * world,
+            "ms_per_step": per,
+            # both directions run at once: bytes moved per second over all ranks, copies alone against the full step
+            "link_ceiling_ms_per_step": ceiling_ms, "link_ceiling_gbs": moved / (ceiling_ms * 1e-3) / 1e9,
+            "link_achieved_gbs": moved / (per * 1e-3) / 1e9}
+
+
+def release():
+    """Free the previous workload's device memory and compiled graphs (the caller drops its reference first)."""
+    import gc
+
+    gc.collect()
+    torch._dynamo.reset()
+    torch.cuda.empty_cache()
 
 
 def main():
@@ -534,8 +728,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg4", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"],
+                    help="strong: the configuration's rows are split over the GPUs; weak: every GPU gets all of them")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only (no `workloads` sub-records)")
     ap.add_argument("--no-graph", action="store_true", help="do not capture launch-bound steps in CUDA graphs")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -561,124 +757,76 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    from fuseml_b200 import _native, build as _build, kernels as K
+    from fuseml_b200 import _native, build as _build
 
     _build.build()
     _native.load()
     W = max(3, args.warmup)
     steps = max(1, args.steps)
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    wl = make_workload(args.workload, world, args.scaling)
+    h = Harness(dist, ClockSampler(local_rank))
+    peaks, peak_src = load_peaks()
+    use_graph = not args.no_graph
+    name = args.workload
+    scaling = args.scaling if name in SHARDED else "weak"
 
-    def barrier():
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    wl = make_workload(name, world, scaling)
+    head = measure(h, wl, name, W, steps, use_graph, peaks, peak_src, world)
+    e2e = measure_e2e(h, wl, steps, world)
+    wl = None
+    release()
 
-    def timed(fn, n, finish=None):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n):
-            fn()
-        if finish is not None:
-            finish()          # make the timing stream wait for work enqueued on other streams
-        e1.record()
-        torch.cuda.synchronize()
-        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-        if dist is not None:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        barrier()
-        return float(ms.item())
+    extras = {}
+    if not args.no_extras:
+        if world > 1 and name == "cfg4" and scaling == "strong":
+            # the replica case beside the sharded one: every GPU runs the whole 8192-token block
+            wl = make_workload("cfg4", world, "weak")
+            m = measure(h, wl, "cfg4", 3, steps, use_graph, peaks, peak_src, world, sustained_s=0)
+            extras["cfg4_replicas"] = {"scaling": "weak", "rows_per_gpu": wl.tokens, "ms_per_step": m["ms_per_step"],
+                                       "tokens_per_s": m["tokens_per_s"], "roofline": m["roofline"]}
+            wl = None
+            release()
+        others = [n for n in ("cfg5", "cfg3", "cfg2", "cfg1") if n != name and (world == 1 or n in SHARDED)]
+        for other in others:
+            sc = "strong" if other in SHARDED else "weak"
+            wl = make_workload(other, world, sc)
+            m = measure(h, wl, other, 3, 5, use_graph, peaks, peak_src, world)
+            rec = {"config": workload_config(other, world, sc), "dtype": wl.dtype, "cuda_graph": m["cuda_graph"],
+                   "burst": {k: m[k] for k in ("ms_per_step", "steps", "tokens_per_s", "roofline")},
+                   **m["sustained"]}
+            if other == "cfg5" and world > 1:
+                from fuseml_b200.sharding import allreduce_scalars
 
-    for _ in range(W):
-        wl.step()
-    wl.check_compiled()
-    graphed = False
-    if not args.no_graph:
-        try:
-            graphed = wl.use_graphs()
-        except Exception as exc:          # capture is an optimisation, never a requirement
-            print(f"[bench] CUDA graph capture failed, stepping eagerly: {exc!r}", file=sys.stderr)
-            wl.graphs = None
-        for _ in range(3):
-            wl.step()
-    if rank == 0:
-        sampler.wait_for_samples(1)     # started before the workload was built; normally no wait
-    launches_before = wl.fused_launches()
-    total_ms = timed(wl.step, steps)
-    launches_timed = wl.fused_launches() - launches_before
-    if graphed:
-        launches_timed = wl.gemm_launches_per_step * steps     # replays do not pass through the Python counters
-    # The timed region may be shorter than one sampling period (50 ms): repeat the same step,
-    # untimed, so that the window under load is at least 0.4 s.  The count is derived from the
-    # all-reduced time, so every rank runs the same number of steps (and collectives).
-    extra = max(0, int(400.0 / max(total_ms / steps, 1e-3)) - steps)
-    for _ in range(min(extra, 20000)):
-        wl.step()
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else {}
-    if rank == 0:
-        clocks["window"] = "timed region plus untimed repeats of the same step (>= 0.4 s under load)"
-    status = K.device_status()
-    if status != 0:
-        raise SystemExit(f"device status {status:#x}: a bounded wait ran out; numbers would be meaningless")
-
-    for _ in range(2):
-        wl.e2e_step()
-    wl.e2e_finish()
-    e2e_ms = timed(wl.e2e_step, steps, finish=wl.e2e_finish)
+                s, mx = wl.scalars
+                ar_ms, _ = h.timed(lambda: allreduce_scalars(total=s, maximum=mx), 200, clocks=False)
+                rec["allreduce"] = {"ms_per_call": ar_ms / 200, "calls_per_step": 1, "inside_timed_region": True,
+                                    "what": "NCCL all-reduce of the global sum (SUM) and amax (MAX), 4 bytes each"}
+            extras[other] = rec
+            wl = None
+            release()
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    peaks, peak_src = load_peaks()
-    ms_per_step = total_ms / steps
-    value = wl.tokens * world / (ms_per_step * 1e-3)
-    launch_ms = ms_per_step / wl.gemm_launches_per_step  # back-to-back launches of the same kernel on one stream
-    if wl.bound == "tensor":
-        achieved = wl.flops_per_launch / (launch_ms * 1e-3) / 1e12
-        peak = peaks["bf16_tflops_sustained"]
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_kind": f"bf16_tflops_sustained, {peak_src}", "frac_of_burst_peak": achieved / peaks["bf16_tflops"]}
-    else:
-        achieved = wl.algo_bytes / (launch_ms * 1e-3) / 1e9
-        peak = peaks["hbm_gbs"]
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_kind": f"hbm_gbs, {peak_src}"}
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
-    roof["kernel"] = "gemm_epilogue_kernel_v2"
-    roof["launch_us"] = launch_ms * 1e3
-
+    cfg = workload_config(name, world, scaling)
     line = {
-        "metric": "mlp_block_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
-        "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
-        "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.name, "rows_per_gpu": wl.tokens, "global_rows": wl.tokens * world,
-                   "l2": ("9 MB working set, resident in L2: a latency-bound parity configuration, not a roofline claim"
-                          if args.workload == "cfg1" else
-                          "inputs larger than L2 (weights + activations per step exceed 126 MB"
-                          + ("; weight copies rotated)" if args.workload == "cfg2" else ")")),
-                   "parallelism": f"rows sharded over {world} GPU(s), weights replicated",
-                   "cuda_graph": bool(graphed),
-                   "host_affinity": (f"rank 0 bound to the {len(numa_cores)} cores NVML reports local to its GPU"
-                                     if numa_cores else "unchanged")},
-        "e2e": {"value": wl.tokens * world / (e2e_ms / steps * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": wl.h2d_bytes * world, "d2h_bytes_per_step": wl.d2h_bytes * world,
-                "ms_per_step": e2e_ms / steps},
-        "gpu_launches": launches_timed + (steps if wl.launches_per_step > wl.gemm_launches_per_step else 0),
-        "roofline": roof,
-        "clocks": clocks,
-        "tflops": wl.flops * world / (ms_per_step * 1e-3) / 1e12,
+        "metric": "mlp_block_tokens_per_s", "value": head["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": W, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": scaling,
+        "vs_baseline": None, "dtype": {"cfg1": "f32"}.get(name, "bf16"), "data": "synthetic", "config": cfg,
+        "runtime": {"cuda_graph": head["cuda_graph"],
+                    "host_affinity": (f"rank 0 bound to the {len(numa_cores)} cores NVML reports local to its GPU"
+                                      if numa_cores else "unchanged")},
+        "e2e": e2e, "gpu_launches": head["gpu_launches"], "roofline": head["roofline"], "clocks": head["clocks"],
+        "roofline_sustained": {**head["sustained"]["roofline"], "ms_per_step": head["sustained"]["ms_per_step"],
+                               "steps": head["sustained"]["steps"], "clocks": head["sustained"]["clocks"]},
+        "tflops": head["tflops"],
     }
-    if not args.no_cpu_baseline:
+    if extras:
+        line["workloads"] = extras
+    if not args.no_cpu_baseline and world == 1:
         try:
-            v, desc, cores, ms, n = cpu_baseline(args.workload, budget_s=15.0)
+            v, desc, cores, ms, n = cpu_baseline(name, budget_s=15.0)
             line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": desc}
         except Exception as exc:  # the GPU numbers stand on their own
             line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
