@@ -146,9 +146,22 @@ class Workload:
     def e2e_finish(self):
         """Called once after the last e2e step, before the closing event is recorded."""
 
-    def use_graphs(self):
+    #: steps one call of ``step()`` runs (a captured graph may hold several consecutive steps)
+    steps_per_call = 1
+
+    def use_graphs(self, steps_hint=1):
         """Capture the resident step in CUDA graphs where that pays (launch-bound steps)."""
         return False
+
+
+def graph_steps(steps_hint, limit=60):
+    """How many consecutive steps one captured graph holds: the timed step count itself when it is
+    small, else its largest divisor up to `limit` (so that K timed steps are whole replays)."""
+    k = max(1, int(steps_hint))
+    for g in range(min(k, limit), 0, -1):
+        if k % g == 0:
+            return g
+    return 1
 
 
 class MLPBlock(Workload):
@@ -261,21 +274,23 @@ class ActHeavyGemm(Workload):
 
     def step(self):
         if self.graphs is not None:
-            g = self.graphs[self.i % len(self.graphs)]
-            self.i += 1
-            return g()
+            return self.graphs()
         return self._forward(self.x, self.r)
 
-    def use_graphs(self):
-        """One captured graph per weight copy (the step is a single ~50 us kernel: without a
-        graph the host's launch path is part of the measurement)."""
+    def use_graphs(self, steps_hint=1):
+        """One captured graph of several consecutive steps, each on the next copy of the weight (the
+        step is a single kernel of about 35 us: launched one by one, the host's launch path and the
+        gap between two graph launches are part of the measurement; inside a graph the launches
+        keep their programmatic dependency, so a step's set-up overlaps its predecessor's tail)."""
         from fuseml_b200.runtime import GraphedCallable
 
-        graphs = []
-        for W in self.Ws:
-            self.module.W.data = W
-            graphs.append(GraphedCallable(self.compiled, self.x, self.r))
-        self.graphs = graphs
+        g = graph_steps(steps_hint)
+
+        def several(x, r):
+            return [self._forward(x, r) for _ in range(g)]
+
+        self.graphs = GraphedCallable(several, self.x, self.r)
+        self.steps_per_call = g
         return True
 
     def e2e_step(self):
@@ -366,10 +381,16 @@ class SmallFp32MLP(Workload):
     def step(self):
         return self.graph() if self.graph is not None else self._forward(self.x)
 
-    def use_graphs(self):
+    def use_graphs(self, steps_hint=1):
         from fuseml_b200.runtime import GraphedCallable
 
-        self.graph = GraphedCallable(self.compiled, self.x)
+        g = graph_steps(steps_hint)
+
+        def several(x):
+            return [self._forward(x) for _ in range(g)]
+
+        self.graph = GraphedCallable(several, self.x)
+        self.steps_per_call = g
         return True
 
     def e2e_step(self):
@@ -616,17 +637,18 @@ def roofline_of(wl, name, launch_ms, region_s, peaks, peak_src):
     return roof
 
 
-def prepare(wl, W, use_graph):
+def prepare(wl, W, use_graph, steps):
     for _ in range(W):
         wl.step()
     wl.check_compiled()
     graphed = False
     if use_graph:
         try:
-            graphed = wl.use_graphs()
+            graphed = wl.use_graphs(steps)
         except Exception as exc:          # capture is an optimisation, never a requirement
             print(f"[bench] CUDA graph capture failed, stepping eagerly: {exc!r}", file=sys.stderr)
-            wl.graphs = None
+            wl.graphs = wl.graph = None
+            wl.steps_per_call = 1
         for _ in range(3):
             wl.step()
     torch.cuda.synchronize()
@@ -672,9 +694,11 @@ def link_ceiling(h, wl, steps):
 
 def measure(h, wl, name, W, steps, use_graph, peaks, peak_src, world, sustained_s=1.0):
     """K timed steps (the headline numbers) and the same step repeated for `sustained_s` seconds."""
-    graphed = prepare(wl, W, use_graph)
+    graphed = prepare(wl, W, use_graph, steps)
+    spc = wl.steps_per_call            # a captured graph may hold several consecutive steps
+    steps = max(1, steps // spc) * spc
     before = wl.fused_launches()
-    total_ms, clocks = h.timed(wl.step, steps)
+    total_ms, clocks = h.timed(wl.step, steps // spc)
     launches = wl.gemm_launches_per_step * steps if graphed else wl.fused_launches() - before
     launches += steps * (wl.launches_per_step - wl.gemm_launches_per_step)
     check_status()
@@ -683,10 +707,11 @@ def measure(h, wl, name, W, steps, use_graph, peaks, peak_src, world, sustained_
         "ms_per_step": ms_per_step, "steps": steps, "tokens_per_s": wl.tokens * world / (ms_per_step * 1e-3),
         "tflops": wl.flops * world / (ms_per_step * 1e-3) / 1e12,
         "roofline": roofline_of(wl, name, ms_per_step / wl.gemm_launches_per_step, total_ms * 1e-3, peaks, peak_src),
-        "clocks": clocks, "gpu_launches": launches, "cuda_graph": bool(graphed),
+        "clocks": clocks, "gpu_launches": launches, "cuda_graph": bool(graphed), "steps_per_graph": spc if graphed else None,
     }
     if sustained_s:
-        s_ms, n, s_clocks = h.timed_for(wl.step, sustained_s, ms_per_step)
+        s_ms, calls, s_clocks = h.timed_for(wl.step, sustained_s, ms_per_step * spc)
+        n = calls * spc
         check_status()
         out["sustained"] = {
             "ms_per_step": s_ms / n, "steps": n, "tokens_per_s": wl.tokens * world / (s_ms / n * 1e-3),

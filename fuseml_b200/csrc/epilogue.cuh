@@ -110,6 +110,39 @@ __device__ __forceinline__ void sigmoid2(float& x0, float& x1) {
   x1 = rcp_approx(d1);
 }
 
+// gelu_erf(x) * sigmoid(x) of two values with two special-function ops per element instead of
+// four: erf through Abramowitz-Stegun 7.1.28, erfc(|z|) = 1 / P(|z|)^16 with a degree-6
+// polynomial P (|error| < 3e-7, no exponential), and one reciprocal shared with the sigmoid:
+//   r = 1 / (P^16 (1 + 2^(-x log2 e))),  erfc = (1 + 2^(-x log2 e)) r,  sigmoid = P^16 r.
+// z = x / sqrt 2 is folded into the coefficients.  |x| is clamped at 4 sqrt 2 (erf is 1 to fp32
+// beyond) and the exponent at 64 so that the product of the two denominators stays finite.
+// The rest is packed arithmetic on the FMA pipe, which the special-function unit runs beside.
+__device__ __forceinline__ void gelu_erf_times_sigmoid2(float& x0, float& x1) {
+  const f32x2 x = pack2(x0, x1);
+  const f32x2 ax = pack2(fminf(fabsf(x0), 5.65685424949238f), fminf(fabsf(x1), 5.65685424949238f));
+  f32x2 pq = fma2(ax, splat2(0.0000430638f * 0.125f), splat2(0.0002765672f * 0.17677669529663688f));
+  pq = fma2(pq, ax, splat2(0.0001520143f * 0.25f));
+  pq = fma2(pq, ax, splat2(0.0092705272f * 0.35355339059327373f));
+  pq = fma2(pq, ax, splat2(0.0422820123f * 0.5f));
+  pq = fma2(pq, ax, splat2(0.0705230784f * 0.70710678118654752440f));
+  pq = fma2(pq, ax, splat2(1.0f));
+  pq = mul2(pq, pq);
+  pq = mul2(pq, pq);
+  pq = mul2(pq, pq);
+  pq = mul2(pq, pq);                                            // P^16 <= 5.6e7
+  float w0, w1;
+  unpack2(mul2(x, splat2(-1.4426950408889634f)), w0, w1);
+  const f32x2 den = add2(pack2(ex2_approx(fminf(w0, 64.0f)), ex2_approx(fminf(w1, 64.0f))), splat2(1.0f));
+  float q0, q1;
+  unpack2(mul2(pq, den), q0, q1);
+  const f32x2 r = pack2(rcp_approx(q0), rcp_approx(q1));
+  float e0, e1;
+  unpack2(fma2(mul2(den, r), splat2(-1.0f), splat2(1.0f)), e0, e1);   // 1 - erfc(|z|) = |erf z|
+  const f32x2 erf = pack2(copysignf(e0, x0), copysignf(e1, x1));
+  const f32x2 hx = mul2(x, splat2(0.5f));
+  unpack2(mul2(fma2(hx, erf, hx), mul2(pq, r)), x0, x1);
+}
+
 __device__ __forceinline__ float load_scalar(const void* p, int64_t idx, int32_t dtype) {
   if (dtype == FUSEML_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[idx]);
   if (dtype == FUSEML_F16) return __half2float(reinterpret_cast<const __half*>(p)[idx]);
@@ -309,6 +342,10 @@ __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int3
       case FUSEML_OP_SIGMOID:
 #pragma unroll
         for (int i = 0; i < CH; i += 2) sigmoid2(v[i], v[i + 1]);
+        break;
+      case FUSEML_OP_GELU_ERF_MUL_SIGMOID:
+#pragma unroll
+        for (int i = 0; i < CH; i += 2) gelu_erf_times_sigmoid2(v[i], v[i + 1]);
         break;
       case FUSEML_OP_ADD_IMM: {
         const float c = p.ops[op].imm;

@@ -147,6 +147,39 @@ static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 #undef FUSEML_DISPATCH
 }
 
+// Peephole over the epilogue program: the diamond gelu_erf(h) * sigmoid(h), written with the
+// second value register as SAVE, GELU_ERF, SWAP, SIGMOID, MUL_SAVED (or with the two branches
+// the other way round), becomes the single op FUSEML_OP_GELU_ERF_MUL_SIGMOID, which shares one
+// reciprocal between the two functions.  Only when `saved` is not read again before the next
+// SAVE: the fused op leaves it untouched.  Returns the new length.
+static int fuse_diamonds(const fuseml_epi_op_t* in, int n, fuseml_epi_op_t* out) {
+  int m = 0;
+  for (int i = 0; i < n; ++i) {
+    if (i + 4 < n && in[i].opcode == FUSEML_OP_SAVE && in[i + 2].opcode == FUSEML_OP_SWAP &&
+        in[i + 4].opcode == FUSEML_OP_MUL_SAVED &&
+        ((in[i + 1].opcode == FUSEML_OP_GELU_ERF && in[i + 3].opcode == FUSEML_OP_SIGMOID) ||
+         (in[i + 1].opcode == FUSEML_OP_SIGMOID && in[i + 3].opcode == FUSEML_OP_GELU_ERF))) {
+      bool dead = true;
+      for (int j = i + 5; j < n; ++j) {
+        const int32_t oc = in[j].opcode;
+        if (oc == FUSEML_OP_SAVE) break;
+        if (oc == FUSEML_OP_SWAP || oc == FUSEML_OP_ADD_SAVED || oc == FUSEML_OP_MUL_SAVED) { dead = false; break; }
+      }
+      if (dead) {
+        out[m] = in[i];
+        out[m].opcode = FUSEML_OP_GELU_ERF_MUL_SIGMOID;
+        out[m].slot = 0;
+        out[m].imm = 0.0f;
+        ++m;
+        i += 4;
+        continue;
+      }
+    }
+    out[m++] = in[i];
+  }
+  return m;
+}
+
 static int check_plan(const fuseml_plan_t* pl) {
   if (pl->tile_m != 128) return FUSEML_E_PLAN;
   if (pl->tile_n < 32 || pl->tile_n > 256 || pl->tile_n % 32 != 0) return FUSEML_E_PLAN;
@@ -314,11 +347,10 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   p.d = desc->d;
   p.ldd = desc->ldd;
   p.out_dtype = desc->out_dtype;
-  p.n_ops = desc->n_ops;
-  for (int i = 0; i < desc->n_ops; ++i) {
-    p.ops[i] = desc->ops[i];
+  p.n_ops = fuse_diamonds(desc->ops, desc->n_ops, p.ops);
+  for (int i = 0; i < p.n_ops; ++i) {
     p.ops[i].reserved = 0;
-    const int32_t oc = desc->ops[i].opcode;
+    const int32_t oc = p.ops[i].opcode;
     if (oc == FUSEML_OP_SAVE || oc == FUSEML_OP_SWAP || oc == FUSEML_OP_ADD_SAVED || oc == FUSEML_OP_MUL_SAVED)
       p.uses_saved = 1;
   }
@@ -334,10 +366,10 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   p.mat_slot = -1;
   {
     int n_vec = 0;
-    for (int i = 0; i < desc->n_ops; ++i) {
-      const int32_t oc = desc->ops[i].opcode;
+    for (int i = 0; i < p.n_ops; ++i) {
+      const int32_t oc = p.ops[i].opcode;
       if (oc != FUSEML_OP_ADD_T && oc != FUSEML_OP_MUL_T) continue;
-      const int32_t slot = desc->ops[i].slot;
+      const int32_t slot = p.ops[i].slot;
       const fuseml_operand_t& o = desc->operands[slot];
       if (o.stride_m == 0 && o.stride_n == 1) {
         int idx = -1;

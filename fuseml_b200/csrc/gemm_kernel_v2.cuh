@@ -37,6 +37,7 @@ enum : int32_t {
   kWhereEpilogueTmemFull = 0x204,
   kWhereProducerDrain = 0x205,
   kWhereEpilogueTileIn = 0x206,
+  kWhereStoreBox = 0x207,
 };
 
 // Optional stall counters (diagnostic builds only, -DFUSEML_STALL_COUNTERS): per CTA
@@ -46,7 +47,7 @@ enum : int32_t {
 //   [6] wall clock (ns) at kernel entry                [7] wall clock (ns) just before the CTA exits
 //   [8] ... after set-up (barriers, TMEM, cluster sync) [9] ... when the MMA thread has issued everything
 //   [10] ... when epilogue warp 2 is done               [11] ... after the tear-down barriers
-//   [12..15] epilogue warp 2, cycles: TMEM load | epilogue program | store / tile write | final barrier + TMA store
+//   [12..15] epilogue warp 2, cycles: TMEM load | epilogue program | store / tile write | unused
 #ifdef FUSEML_STALL_COUNTERS
 __device__ unsigned long long g_stall[1024][16];
 #define FUSEML_STALL_T0() const long long stall_t0 = clock64()
@@ -65,7 +66,7 @@ struct Smem {
   static constexpr int kColRedBytes = 4 * 2 * BN * 4;             // [quarter][sum|max][BN]
   static constexpr int kStagedBytes = 2 * 2 * BN * 4;             // [acc buffer][row vector][BN] fp32
   static constexpr int kBarOffset = kRingBytes + kColRedBytes + kStagedBytes;
-  static constexpr int kNumBars = 2 * STAGES + 5;                 // ring full/empty, TMEM full/empty x 2, tile I/O
+  static constexpr int kNumBars = 2 * STAGES + 5 + 4;             // ring full/empty, TMEM full/empty x 2, tile in, 4 output boxes
   static constexpr int kTotalBytes = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kDynamicBytes = kTotalBytes + 1024;
 };
@@ -156,6 +157,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
   const uint32_t tile_in_bar = bar_base + 8u * (2 * STAGES + 4);
+  auto box_bar = [&](int j) { return bar_base + 8u * (2 * STAGES + 5 + j); };   // output box j written by all epilogue warps
   // tile I/O through the drained ring (sixteen-warp instance only; see GemmParams::io_flags)
   // (only when every tile walker really has at most one tile: the launch may have been given
   // fewer CTA pairs than the host asked for)
@@ -190,6 +192,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       ptx::mbar_init(tmem_empty_bar(a), kEpiWarps * CG);   // leader collects both CTAs' epilogue warps
     }
     ptx::mbar_init(tile_in_bar, 1);
+    for (int j = 0; j < 4; ++j) ptx::mbar_init(box_bar(j), kEpiWarps);
     *abort_flag = 0u;
     ptx::fence_mbar_init();
   }
@@ -325,6 +328,27 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             ptx::tma_load_2d(smem_base + j * kBoxBytes, &tmap_r, tile_in_bar, n_tile0 + j * 64, m0);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
+      }
+      if (EW == 16 && tile_out && ok && unit < p.num_tiles) {
+        // This CTA's only tile, on its way out: every 64-column box of the output tile is written
+        // to the drained ring by all epilogue warps (one arrival each on the box's barrier); this
+        // thread, idle by now, stores each box as soon as it is complete, so that only the last
+        // box's store is left when the epilogue warps finish and nobody waits at a CTA barrier.
+        int32_t tm, tn;
+        tile_coords(unit, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
+        const int32_t row0 = (tm * CG + static_cast<int32_t>(cta_rank)) * kTileM;
+        const int32_t n_tile0 = tn * bn;
+        for (int j = 0; j < tile_boxes; ++j) {
+          if (!ptx::mbar_wait(box_bar(j), 0u, abort_flag, p.status, kWhereStoreBox, true)) {
+            ok = false;
+            break;
+          }
+          if (n_tile0 + j * 64 < p.N) {
+            ptx::tma_store_2d(&tmap_d, smem_base + j * kBoxBytes, n_tile0 + j * 64, row0);
+            ptx::bulk_commit_group();
+          }
+        }
+        ptx::bulk_wait_read_all();   // the boxes must stay in shared memory until the copies have read them
       }
 #ifdef FUSEML_STALL_COUNTERS
       g_stall[blockIdx.x][5] = st_empty;
@@ -492,7 +516,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       ptx::tc_fence_after_sync();
       float row_sum = 0.0f, row_max = -INFINITY;
       // Tile I/O through shared memory (see GemmParams::io_flags): every warp then walks all its
-      // chunks, active or not, because each 64-column box ends in a barrier of all epilogue warps.
+      // chunks, active or not, because the storing thread counts sixteen arrivals per 64-column box.
       const bool staged_io = tile_in || tile_out;
       if (tile_in && ok &&
           !ptx::mbar_wait(tile_in_bar, 0u, abort_flag, p.status, kWhereEpilogueTileIn, true)) {
@@ -590,28 +614,15 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             }
           }
         }
-      }
-#ifdef FUSEML_STALL_COUNTERS
-      const long long c3 = clock64();
-#endif
-      if (EW == 16 && tile_out) {
-        // One barrier for the whole tile, not one per box: a barrier per 64 columns re-aligns
-        // the sixteen warps at every chunk, and warps in lock step queue up on the special-
-        // function unit instead of overlapping one warp's exp/rcp with another's FMAs.
-        ptx::fence_proxy_async_smem();
-        asm volatile("bar.sync 3, %0;" ::"n"(32 * EW) : "memory");
-        if (threadIdx.x == 64 && ok) {
-          for (int j = 0; j < tile_boxes; ++j) {
-            const int32_t box_n0 = n_tile0 + j * 64;
-            if (box_n0 < p.N) ptx::tma_store_2d(&tmap_d, smem_base + j * kBoxBytes, box_n0, tm128 * kTileM);
-          }
-          ptx::bulk_commit_group();
-          ptx::bulk_wait_all();
+        if (EW == 16 && tile_out) {
+          // this warp's share of output box c / 4 is in shared memory (or the chunk lies past N):
+          // publish it to the async proxy and tell the storing thread.  No CTA-wide barrier: the
+          // sixteen warps stay out of step, one warp's exp/rcp overlapping another's FMAs.
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(box_bar(c >> 2));
         }
       }
-#ifdef FUSEML_STALL_COUNTERS
-      st_tail += clock64() - c3;
-#endif
       // accumulator drained: hand the TMEM buffer back to the (leader's) MMA thread
       ptx::tc_fence_before_sync();
       __syncwarp();

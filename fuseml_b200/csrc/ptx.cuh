@@ -145,6 +145,9 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // waits until every bulk group of this thread has completed (reads of shared memory and writes
 // to global memory)
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// waits only until every bulk group of this thread has finished reading its shared-memory source
+// (the global writes complete on their own; they are visible when the kernel ends)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // Same, with an L2 cache-policy hint (created by createpolicy).
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* tm, uint32_t bar,
                                                  int32_t c0, int32_t c1, uint64_t policy) {

@@ -52,6 +52,11 @@ class EpilogueProgram:
     def sigmoid(self) -> "EpilogueProgram":
         return self._push(N.OP_SIGMOID)
 
+    def gelu_times_sigmoid(self) -> "EpilogueProgram":
+        """``acc = gelu(acc) * sigmoid(acc)`` as one step (what the launch rewrites the diamond
+        ``save, gelu, swap, sigmoid, mul_saved`` to)."""
+        return self._push(N.OP_GELU_ERF_MUL_SIGMOID)
+
     # --- binary with a python scalar ------------------------------------------
     def add_scalar(self, c: float) -> "EpilogueProgram":
         return self._push(N.OP_ADD_IMM, imm=float(c))

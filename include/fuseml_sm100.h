@@ -80,7 +80,11 @@ enum {
                              /*   writable, row-major, same dtype rules as the output   */
   FUSEML_OP_SUB_T = 14,      /* acc -= operand[slot][m,n]                               */
   FUSEML_OP_RSUB_T = 15,     /* acc = operand[slot][m,n] - acc                          */
-  FUSEML_OP__COUNT = 16
+  FUSEML_OP_GELU_ERF_MUL_SIGMOID = 16, /* acc = gelu_erf(acc) * sigmoid(acc) in one step: the   */
+                             /*   diamond SAVE, GELU_ERF, SWAP, SIGMOID, MUL_SAVED (either     */
+                             /*   branch order) is rewritten to it at launch when `saved` is   */
+                             /*   not read again; half the special-function work              */
+  FUSEML_OP__COUNT = 17
 };
 
 #define FUSEML_MAX_EPI_OPS 16

@@ -109,7 +109,7 @@ def _bcast(t: np.ndarray, M: int, N: int) -> np.ndarray:
 def run_epilogue(acc: np.ndarray, ops: Sequence[tuple], aux_dtype: str = "bf16"):
     """Apply ``ops`` in order.  Each op is a tuple:
 
-    ``("relu",)``, ``("gelu",)``, ``("gelu_tanh",)``, ``("sigmoid",)``,
+    ``("relu",)``, ``("gelu",)``, ``("gelu_tanh",)``, ``("sigmoid",)``, ``("gelu_times_sigmoid",)``,
     ``("add_scalar", c)``, ``("mul_scalar", c)``,
     ``("add", t)``, ``("mul", t)``, ``("sub", t)``, ``("rsub", t)`` with an external array,
     ``("save",)``, ``("swap",)``, ``("add_saved",)``, ``("mul_saved",)``,
@@ -131,6 +131,8 @@ def run_epilogue(acc: np.ndarray, ops: Sequence[tuple], aux_dtype: str = "bf16")
             v = gelu_tanh(v)
         elif k == "sigmoid":
             v = sigmoid(v)
+        elif k == "gelu_times_sigmoid":
+            v = (gelu_erf(v).astype(np.float64) * sigmoid(v).astype(np.float64)).astype(np.float32)
         elif k == "add_scalar":
             v = (v + np.float32(op[1])).astype(np.float32)
         elif k == "mul_scalar":

@@ -255,6 +255,9 @@ EPILOGUES = {
     "sub_rsub": lambda: [("sub", "row"), ("rsub", "full")],
     "dag_gelu_mul_sigmoid_add": lambda: [("bias", "row"), ("save",), ("gelu",), ("swap",), ("sigmoid",),
                                          ("mul_saved",), ("add", "full")],
+    "dag_sigmoid_first": lambda: [("bias", "row"), ("save",), ("sigmoid",), ("swap",), ("gelu",), ("mul_saved",)],
+    "dag_saved_read_again": lambda: [("save",), ("gelu",), ("swap",), ("sigmoid",), ("mul_saved",), ("add_saved",)],
+    "gelu_times_sigmoid_op": lambda: [("bias", "row"), ("gelu_times_sigmoid",), ("add", "full")],
     "dag_add_saved": lambda: [("save",), ("relu",), ("add_saved",)],
     "long_chain": lambda: [("bias", "row"), ("relu",), ("mul_scalar", 2.0), ("add", "full"), ("sigmoid",),
                            ("mul", "col"), ("add_scalar", -0.25), ("gelu",)],
