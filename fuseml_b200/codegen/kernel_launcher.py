@@ -273,6 +273,14 @@ class KernelLauncher:
             input_tensors = tuple(self._materialize_if_needed(t) for t in input_tensors)
         if self._lib is None:
             self._lib = N.load()
+        # TMA reads A and B in place and needs 16-byte aligned bases.  The compile-time check
+        # sees shapes and strides only; a live tensor may still be a view that starts in the
+        # middle of a 16-byte word (a column slice).  Such an operand is copied once into a fresh,
+        # aligned buffer (as negative strides are), and the fused kernel runs on the copy.
+        li, ri = self._left_idx, self._right_idx
+        if (input_tensors[li].data_ptr() | input_tensors[ri].data_ptr()) & 15 and input_tensors[li].dtype != torch.float32:
+            input_tensors = tuple(t.clone(memory_format=torch.contiguous_format)
+                                  if i in (li, ri) and t.data_ptr() & 15 else t for i, t in enumerate(input_tensors))
         key = tuple((t.shape, t.stride()) for t in input_tensors)
         p = self._prepared.get(key)
         if p is None:

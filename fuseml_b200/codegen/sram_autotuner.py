@@ -10,13 +10,12 @@ around what constrains a tcgen05 kernel:
   tile overlap the MMAs of the next);
 * UMMA shape: M = 128 per CTA, N a multiple of 16 up to 256, ``BK * bytes == 128`` (one swizzle row).
 
-``get_best_config`` scores candidates with the roofline estimate the native planner uses
-(tensor time of the tiles in waves vs. HBM time); the authoritative decision at launch is
-``fuseml_sm100_plan`` — this class exposes the same model to Python callers and tests.
+``get_best_config`` returns what the native router (``fuseml_sm100_plan``, the code that
+decides at launch) picks for the problem under this tuner's budgets — tile, ring depth, CTA
+pairs and split-K included; the functions above it are the budget arithmetic alone.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Generator
 
@@ -45,6 +44,9 @@ class TuneConfig:
     sram_bytes: int
     tmem_cols: int = 0
     cluster: int = 1
+    split_k: int = 1
+    bound: str = ""          # "hbm" | "tensor" | "latency": which roofline the router expects to bind
+    t_est_us: float = 0.0
 
 
 def compute_sram_bytes(block_m: int, block_n: int, block_k: int, dtype_bytes: int, num_stages: int) -> int:
@@ -85,35 +87,43 @@ class SRAMAutotuner:
         self.hbm_gbs = hbm_gbs
         self._cache: dict[tuple, TuneConfig] = {}
 
-    def _score_config(self, cfg: TuneConfig, M: int, N: int, K: int, bpe: int) -> float:
-        """Estimated microseconds (lower is better)."""
-        tiles = math.ceil(M / cfg.block_m) * math.ceil(N / cfg.block_n)
-        waves = math.ceil(tiles / self.sm_count)
-        k_pad = math.ceil(K / cfg.block_k) * cfg.block_k
-        rate = self.tensor_tflops * 1e12 / self.sm_count * (0.5 if bpe == 4 else 1.0)
-        t_tile = 2.0 * cfg.block_m * cfg.block_n * k_pad / rate * 1e6
-        t_hbm = bpe * (M * K + K * N + M * N) / (self.hbm_gbs * 1e9) * 1e6
-        # a ring too shallow to cover the load latency leaves the tensor pipe waiting
-        depth_penalty = 1.0 + max(0, 4 - cfg.num_stages) * 0.15
-        narrow_penalty = {256: 1.0, 128: 1.05, 64: 1.15}.get(cfg.block_n, 1.2)
-        return max(waves * t_tile * depth_penalty * narrow_penalty, t_hbm)
-
     def get_best_config(self, M: int, N: int, K: int, dtype: torch.dtype = torch.bfloat16) -> TuneConfig:
+        """The native router's plan for an ``M x N x K`` GEMM of ``dtype`` operands (nn.Linear
+        layout) under this tuner's shared-memory budget, SM count and peaks.  Host only."""
         key = (int(M), int(N), int(K), dtype)
         hit = self._cache.get(key)
         if hit is not None:
             return hit
+        import ctypes as C
+
+        from .. import _native as N_
+        from ..kernels import dtype_code
+
+        lib = N_.load()
         bpe = _DTYPE_BYTES.get(dtype, 4)
-        best, best_t = None, float("inf")
-        for cfg in generate_sram_safe_configs(dtype, self.sram_budget):
-            if cfg.block_n == 64:
-                continue  # no 64-wide kernel instance is built
-            t = self._score_config(cfg, M, N, K, bpe)
-            # prefer deeper rings at equal time
-            if t < best_t - 1e-9 or (abs(t - best_t) <= 1e-9 and best is not None and cfg.num_stages > best.num_stages):
-                best, best_t = cfg, t
-        if best is None:
+        code = dtype_code(dtype)
+        desc = N_.GemmDesc()
+        desc.M, desc.N, desc.K = int(M), int(N), int(K)
+        desc.a, desc.b, desc.d = 0x1000, 0x2000, 0x3000          # layout-only query: aligned dummies
+        ld = int(K) if (code == N_.F32 or (K * bpe) % 16 == 0) else (int(K) * bpe + 15) // 16 * 16 // bpe
+        desc.lda, desc.b_stride_k, desc.b_stride_n, desc.ldd = ld, 1, ld, int(N)
+        desc.ab_dtype = desc.out_dtype = code
+        props = N_.DeviceProps()
+        lib.fuseml_sm100_query(C.byref(props))                     # published B200 figures when there is no device
+        props.sm_count = self.sm_count
+        props.smem_per_block_optin = self.sram_budget + _FIXED_SMEM
+        props.tensor_tflops, props.hbm_gbs = self.tensor_tflops, self.hbm_gbs
+        plan = N_.Plan()
+        rc = lib.fuseml_sm100_plan(C.byref(desc), C.byref(props), C.byref(plan))
+        if rc != N_.OK:
+            raise ValueError(f"the router rejects {M} x {N} x {K} {dtype}: {N_.strerror(rc)}")
+        kernel_bn = 256 if plan.tile_n > 128 else 128              # the instance that runs the tile
+        stage = (plan.tile_m * plan.tile_k + plan.tile_k * (kernel_bn // plan.cluster)) * (4 if code == N_.F32 else bpe)
+        if plan.stages * stage > self.sram_budget:
             raise ValueError(f"no configuration fits a shared-memory budget of {self.sram_budget} bytes")
+        best = TuneConfig(plan.tile_m, plan.tile_n, plan.tile_k, 2 + 8, plan.stages, plan.stages * stage,
+                          plan.tmem_cols, plan.cluster, max(1, plan.split_k),
+                          ("hbm", "tensor", "latency")[plan.bound], plan.t_est_us)
         self._cache[key] = best
         return best
 

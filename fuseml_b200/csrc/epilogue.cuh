@@ -315,10 +315,73 @@ __device__ __forceinline__ void store_chunk(void* base_ptr, int64_t row_off, int
 // `staged` points at this chunk's columns of the row vectors staged in shared memory
 // (vector j at staged + j * staged_stride); `mat_piece`, when not null, at this thread's 16
 // columns of the matrix operand in a swizzled shared-memory box (ops with reserved == 3).
-template <bool kUsesSaved, int CH>
+// How the program is executed (a template argument of the kernels): by the interpreter below,
+// without or with the second value register, or as straight-line code for the chains the
+// benchmark configurations lower to.  In the interpreter every op is a basic block of its own:
+// the loads of an op cannot start before the previous op's arithmetic has drained, and a cheap
+// op (bias add, residual add) costs several hundred cycles per chunk in dispatch and exposed
+// latency (measured: 323 and 590 cycles per 16-column chunk for four warps per scheduler).  The
+// straight-line forms fetch their operands first and leave the scheduling to the compiler.
+enum : int {
+  kProgGeneric = 0,        // interpreter, no SAVE / SWAP / *_SAVED in the program
+  kProgGenericSaved = 1,   // interpreter with the second value register
+  kProgBiasGelu = 2,       // ADD_T(staged row vector), GELU_ERF
+  kProgBiasAdd = 3,        // ADD_T(staged row vector), ADD_T(matrix)
+  kProgBiasGeluSigAdd = 4, // ADD_T(staged row vector), GELU_ERF_MUL_SIGMOID, ADD_T(matrix)
+  kProgCount = 5
+};
+
+template <int PROG, int CH>
 __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int32_t n0, bool row_ok,
                                             float (&v)[CH], const float* staged, int32_t staged_stride,
                                             const uint8_t* mat_piece = nullptr) {
+  if constexpr (PROG >= kProgBiasGelu) {
+    // ---- straight-line forms: operands first, then the arithmetic ----
+    constexpr int kMatOp = (PROG == kProgBiasAdd) ? 1 : 2;       // index of the matrix ADD_T
+    float4 bias[CH / 4];
+#pragma unroll
+    for (int i = 0; i < CH / 4; ++i) bias[i] = reinterpret_cast<const float4*>(staged)[i];
+    uint4 mat[2];
+    bool mat_regs = false;
+    if constexpr (PROG != kProgBiasGelu && CH == 16) {
+      if (mat_piece != nullptr) {
+        mat[0] = *reinterpret_cast<const uint4*>(mat_piece);
+        mat[1] = *reinterpret_cast<const uint4*>(reinterpret_cast<uintptr_t>(mat_piece) ^ 16u);
+        mat_regs = true;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < CH / 4; ++i) {
+      unpack2(add2(pack2(v[4 * i + 0], v[4 * i + 1]), pack2(bias[i].x, bias[i].y)), v[4 * i + 0], v[4 * i + 1]);
+      unpack2(add2(pack2(v[4 * i + 2], v[4 * i + 3]), pack2(bias[i].z, bias[i].w)), v[4 * i + 2], v[4 * i + 3]);
+    }
+    if constexpr (PROG == kProgBiasGelu) {
+#pragma unroll
+      for (int i = 0; i < CH; i += 2) gelu_erf2(v[i], v[i + 1]);
+    } else {
+      if constexpr (PROG == kProgBiasGeluSigAdd) {
+#pragma unroll
+        for (int i = 0; i < CH; i += 2) gelu_erf_times_sigmoid2(v[i], v[i + 1]);
+      }
+      const EpiOperand& mo = p.operands[p.ops[kMatOp].slot];
+      if (mat_regs) {
+        if constexpr (CH == 16) {
+          const uint32_t w[8] = {mat[0].x, mat[0].y, mat[0].z, mat[0].w, mat[1].x, mat[1].y, mat[1].z, mat[1].w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float2 f;
+            if (mo.dtype == FUSEML_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+            else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            unpack2(add2(pack2(v[2 * j], v[2 * j + 1]), pack2(f.x, f.y)), v[2 * j], v[2 * j + 1]);
+          }
+        }
+      } else if (row_ok) {
+        fold_operand_chunk<CH>(v, FUSEML_OP_ADD_T, mo, m, n0, p.N);
+      }
+    }
+    return;
+  }
+  constexpr bool kUsesSaved = (PROG == kProgGenericSaved);
   float s[kUsesSaved ? CH : 1];
   if (kUsesSaved) {
 #pragma unroll

@@ -73,11 +73,11 @@ struct InstanceState {
   int max_clusters[kMaxDevices] = {0};
 };
 
-template <int BN, int STAGES, int FMT, bool B_MN, bool SAVED, int CG, int EW>
+template <int BN, int STAGES, bool B_MN, int PROG, int CG, int EW>
 static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tr, const CUtensorMap& td,
                            const GemmParams& p, int grid, cudaStream_t stream) {
   using L = v2::Smem<BN, STAGES, CG>;
-  auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, FMT, B_MN, SAVED, CG, EW>;
+  auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, B_MN, PROG, CG, EW>;
   static InstanceState state;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return FUSEML_E_DEVICE; }
@@ -134,16 +134,35 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const C
   return FUSEML_OK;
 }
 
+// Which execution form of the epilogue program a launch uses (epi::kProg*): the straight-line
+// forms need the exact op sequence with the row vector staged in shared memory (reserved == 1)
+// and a matrix operand that is not a staged row vector.
+static int classify_program(const GemmParams& p) {
+  if (p.uses_saved) return epi::kProgGenericSaved;
+  auto is = [&](int i, int32_t opcode) { return p.ops[i].opcode == opcode; };
+  auto staged_vec = [&](int i) { return is(i, FUSEML_OP_ADD_T) && p.ops[i].reserved == 1; };
+  auto matrix_add = [&](int i) { return is(i, FUSEML_OP_ADD_T) && (p.ops[i].reserved == 0 || p.ops[i].reserved == 3); };
+  if (p.n_ops == 2 && staged_vec(0) && is(1, FUSEML_OP_GELU_ERF)) return epi::kProgBiasGelu;
+  if (p.n_ops == 2 && staged_vec(0) && matrix_add(1)) return epi::kProgBiasAdd;
+  if (p.n_ops == 3 && staged_vec(0) && is(1, FUSEML_OP_GELU_ERF_MUL_SIGMOID) && matrix_add(2)) return epi::kProgBiasGeluSigAdd;
+  return epi::kProgGeneric;
+}
+
 template <int BN, int STAGES, int CG, int EW = 8>
 static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tr, const CUtensorMap& td,
-                     const GemmParams& p, int fmt, bool b_mn, int grid, cudaStream_t stream) {
-  const bool saved = p.uses_saved != 0;
-#define FUSEML_DISPATCH(F, MN)                                                              \
-  return saved ? launch_instance<BN, STAGES, F, MN, true, CG, EW>(ta, tb, tr, td, p, grid, stream)  \
-               : launch_instance<BN, STAGES, F, MN, false, CG, EW>(ta, tb, tr, td, p, grid, stream)
-  if (fmt == 2) { FUSEML_DISPATCH(2, false); }
-  if (fmt == 1) { if (b_mn) { FUSEML_DISPATCH(1, true); } else { FUSEML_DISPATCH(1, false); } }
-  if (b_mn) { FUSEML_DISPATCH(0, true); } else { FUSEML_DISPATCH(0, false); }
+                     const GemmParams& p, bool b_mn, int grid, cudaStream_t stream) {
+#define FUSEML_DISPATCH(PROG)                                                                             \
+  case PROG:                                                                                              \
+    return b_mn ? launch_instance<BN, STAGES, true, PROG, CG, EW>(ta, tb, tr, td, p, grid, stream)        \
+                : launch_instance<BN, STAGES, false, PROG, CG, EW>(ta, tb, tr, td, p, grid, stream)
+  switch (classify_program(p)) {
+    FUSEML_DISPATCH(epi::kProgGenericSaved);
+    FUSEML_DISPATCH(epi::kProgBiasGelu);
+    FUSEML_DISPATCH(epi::kProgBiasAdd);
+    FUSEML_DISPATCH(epi::kProgBiasGeluSigAdd);
+    default:
+      FUSEML_DISPATCH(epi::kProgGeneric);
+  }
 #undef FUSEML_DISPATCH
 }
 
@@ -338,6 +357,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   p.N = static_cast<int32_t>(desc->N);
   p.K = static_cast<int32_t>(K);
   const int CGr = plan.cluster;
+  p.fmt = fmt;
   p.tiles_m = static_cast<int32_t>((desc->M + kTileM * CGr - 1) / (kTileM * CGr));
   p.tiles_n = static_cast<int32_t>((desc->N + BN - 1) / BN);
   p.num_tiles = p.tiles_m * p.tiles_n;
@@ -415,8 +435,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     std::memset(&none, 0, sizeof(none));
     const int items = p.num_tiles * slices;
     if (slices > 1) {
-      if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, none, none, pg, fmt, b_mn, items, stream);
-      else rc = launch_bn<128, 6, 1>(ta, tb, none, none, pg, fmt, b_mn, items, stream);
+      if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, none, none, pg, b_mn, items, stream);
+      else rc = launch_bn<128, 6, 1>(ta, tb, none, none, pg, b_mn, items, stream);
       if (rc != FUSEML_OK) return rc;
       GemmParams pf = p;
       pf.split_k = slices;
@@ -464,12 +484,12 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
         encode_2d(&td, p.out_dtype, p.d, desc->M, desc->N, p.ldd, 64, kTileM) == FUSEML_OK) {
       p.io_flags |= 2;
     }
-    if (CGr == 2) rc = launch_bn<256, 6, 2, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
-    else if (BN > 128) rc = launch_bn<256, 4, 1, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
-    else rc = launch_bn<128, 6, 1, 16>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
-  } else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
-  else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
-  else rc = launch_bn<128, 6, 1>(ta, tb, tr, td, p, fmt, b_mn, grid, stream);
+    if (CGr == 2) rc = launch_bn<256, 6, 2, 16>(ta, tb, tr, td, p, b_mn, grid, stream);
+    else if (BN > 128) rc = launch_bn<256, 4, 1, 16>(ta, tb, tr, td, p, b_mn, grid, stream);
+    else rc = launch_bn<128, 6, 1, 16>(ta, tb, tr, td, p, b_mn, grid, stream);
+  } else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, tr, td, p, b_mn, grid, stream);
+  else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, tr, td, p, b_mn, grid, stream);
+  else rc = launch_bn<128, 6, 1>(ta, tb, tr, td, p, b_mn, grid, stream);
   if (rc != FUSEML_OK) return rc;
 
   if (desc->reduce.kinds != 0) {

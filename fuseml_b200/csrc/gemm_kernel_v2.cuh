@@ -18,6 +18,8 @@
 // 1178-1593) and its cuBLAS Lt call sites (fuseml/codegen/cublas_epilogue.py:602-676).
 #pragma once
 
+#include <type_traits>
+
 #include "epilogue.cuh"
 #include "gemm_params.cuh"
 #include "ptx.cuh"
@@ -124,26 +126,27 @@ __device__ __forceinline__ void prefetch_operands(const GemmParams& p, int64_t m
   }
 }
 
-// FMT: 0 = f16, 1 = bf16, 2 = tf32 (fp32 storage).  B_MN: B is row-major [K,N] in global
-// memory (MN-major tiles) instead of K-major.  CG: CTAs per tile (1 or 2).
-template <int BN, int STAGES, int FMT, bool B_MN, bool USES_SAVED, int CG, int EW>
+// B_MN: B is row-major [K,N] in global memory (MN-major tiles) instead of K-major.  PROG: how
+// the epilogue program runs (epi::kProg*).  CG: CTAs per tile (1 or 2).  EW: epilogue warps.
+// The operand format (f16 / bf16 / tf32) is a run-time value (GemmParams::fmt): it only selects
+// the instruction descriptor, the MMA kind and the K extent of a stage.
+template <int BN, int STAGES, bool B_MN, int PROG, int CG, int EW>
 __global__ void __launch_bounds__(threads_for(EW), 1)
 gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_d,
                         const __grid_constant__ GemmParams p) {
   using L = Smem<BN, STAGES, CG>;
-  constexpr int kElemBytes = (FMT == 2) ? 4 : 2;
-  constexpr int BK = kSwizzleBytes / kElemBytes;
-  constexpr int UMMA_K = 32 / kElemBytes;
-  constexpr int kKSteps = BK / UMMA_K;
+  const bool tf32 = p.fmt == 2;
+  const int32_t BK = tf32 ? 32 : 64;             // elements per 128-byte stage row
+  constexpr int kKSteps = 4;                      // MMAs per stage: 32 bytes of K each (16 x 16-bit or 8 x tf32)
   constexpr int BN_CTA = BN / CG;                 // most B columns one CTA loads (sizes shared memory)
   constexpr uint32_t kTmemCols = 2 * BN;
   static_assert(EW == 8 || EW == 16, "two or four epilogue warps per TMEM lane quarter");
   static_assert(EW == 8 || L::kStageBytes % (kTileM * kSwizzleBytes) == 0, "tile I/O packs whole boxes into ring stages");
+  constexpr uint32_t kMnBoxBytes = 64 * kSwizzleBytes;   // MN-major B (16-bit operands only): one 64 k x 64 n box
   constexpr int kEpiWarps = EW;
   constexpr int kEpiSplit = EW / 4;             // warps sharing one TMEM lane quarter
   constexpr int CH = (EW == 16) ? 16 : 32;      // accumulator columns per chunk
-  static_assert(!(B_MN && FMT == 2), "MN-major B is only wired for 16-bit operands");
   static_assert(CG == 1 || CG == 2, "one CTA or a CTA pair");
   static_assert(!B_MN || (BN_CTA % 64 == 0), "MN-major B is loaded in 64-column boxes");
 
@@ -241,7 +244,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   const int32_t bn = p.bn;
   const int32_t bn_cta = bn / CG;
   const int32_t n_boxes = (bn_cta + 63) / 64;                          // MN-major: 64-column TMA boxes
-  const uint32_t stage_tx = L::kABytes + (B_MN ? n_boxes * (BK * kSwizzleBytes) : bn_cta * kSwizzleBytes);
+  const uint32_t stage_tx = L::kABytes + (B_MN ? n_boxes * kMnBoxBytes : bn_cta * kSwizzleBytes);
 
   if (warp == 0) {
     // ------------------------------ TMA producer (every CTA) -----------------------------
@@ -285,10 +288,10 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             } else if (p.b_stream == 0 && n_boxes == BN_CTA / 64) {
 #pragma unroll
               for (int j = 0; j < BN_CTA / 64; ++j)
-                ptx::tma_load_2d(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK);
+                ptx::tma_load_2d(b_dst + j * kMnBoxBytes, &tmap_b, bar, n0 + j * 64, kb * BK);
             } else {
               for (int j = 0; j < n_boxes; ++j)
-                ptx::tma_load_2d_hint(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK, pol_b);
+                ptx::tma_load_2d_hint(b_dst + j * kMnBoxBytes, &tmap_b, bar, n0 + j * 64, kb * BK, pol_b);
             }
           } else {
             if (p.a_stream == 0) ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, kb * BK, m0);
@@ -299,10 +302,10 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             } else if (p.b_stream == 0 && n_boxes == BN_CTA / 64) {
 #pragma unroll
               for (int j = 0; j < BN_CTA / 64; ++j)
-                ptx::tma_load_2d_pair(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK);
+                ptx::tma_load_2d_pair(b_dst + j * kMnBoxBytes, &tmap_b, bar, n0 + j * 64, kb * BK);
             } else {
               for (int j = 0; j < n_boxes; ++j)
-                ptx::tma_load_2d_pair_hint(b_dst + j * (BK * kSwizzleBytes), &tmap_b, bar, n0 + j * 64, kb * BK, pol_b);
+                ptx::tma_load_2d_pair_hint(b_dst + j * kMnBoxBytes, &tmap_b, bar, n0 + j * 64, kb * BK, pol_b);
             }
           }
           ++issued;
@@ -377,8 +380,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ---------------------------
-    if (is_leader && ptx::elect_one()) {
-      const uint32_t idesc = ptx::make_idesc(FMT, 0u, B_MN ? 1u : 0u, kTileM * CG, static_cast<uint32_t>(bn));
+    // The loop body exists twice, once per MMA kind: a test of the format inside the K loop
+    // costs the single issuing thread about 3 % of a tensor-bound GEMM.
+    auto mma_role = [&](auto tf32_tag) {
+      constexpr bool kTf32 = decltype(tf32_tag)::value;
+      const uint32_t idesc = ptx::make_idesc(static_cast<uint32_t>(p.fmt), 0u, B_MN ? 1u : 0u, kTileM * CG, static_cast<uint32_t>(bn));
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -387,7 +393,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       long long st_full = 0, st_tmem = 0;
       bool ready = false;   // the next ring stage is already known to be full
       const uint64_t a_desc0 = ptx::make_smem_desc_sw128(smem_base, 16u, 1024u);
-      const uint64_t b_desc0 = B_MN ? ptx::make_smem_desc_sw128(smem_base + L::kABytes, BK * kSwizzleBytes, 1024u)
+      const uint64_t b_desc0 = B_MN ? ptx::make_smem_desc_sw128(smem_base + L::kABytes, kMnBoxBytes, 1024u)
                                     : ptx::make_smem_desc_sw128(smem_base + L::kABytes, 16u, 1024u);
 #ifdef FUSEML_STALL_COUNTERS
       const long long st_begin = clock64();
@@ -423,15 +429,15 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage) * (L::kStageBytes >> 4);
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage) * (L::kStageBytes >> 4);
           constexpr uint32_t kAStep = 32u >> 4;
-          constexpr uint32_t kBStep = B_MN ? ((UMMA_K * kSwizzleBytes) >> 4) : (32u >> 4);
+          constexpr uint32_t kBStep = B_MN ? ((16 * kSwizzleBytes) >> 4) : (32u >> 4);
 #pragma unroll
           for (int k = 0; k < kKSteps; ++k) {
             const uint32_t accumulate = (kb > kb_begin || k > 0) ? 1u : 0u;
             if (CG == 2) {
-              if (FMT == 2) ptx::mma_tf32_ss_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
+              if (kTf32) ptx::mma_tf32_ss_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
               else ptx::mma_f16_ss_pair(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
             } else {
-              if (FMT == 2) ptx::mma_tf32_ss(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
+              if (kTf32) ptx::mma_tf32_ss(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
               else ptx::mma_f16_ss(d_tmem, a_desc + k * kAStep, b_desc + k * kBStep, idesc, accumulate);
             }
           }
@@ -453,6 +459,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #else
       (void)st_full; (void)st_tmem;
 #endif
+    };
+    if (is_leader && ptx::elect_one()) {
+      if (tf32) mma_role(std::true_type{}); else mma_role(std::false_type{});
     }
     __syncwarp();
   } else {
@@ -555,7 +564,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
           const long long c1 = clock64();
 #endif
-          epi::run_program<USES_SAVED, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
+          epi::run_program<PROG, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
 #ifdef FUSEML_STALL_COUNTERS
           const long long c2 = clock64();
 #endif

@@ -39,6 +39,7 @@ struct GemmParams {
   float* red_sum;    // [partials][len]
   float* red_max;    // [partials][len]
   int32_t uses_saved;  // program contains SAVE/SWAP/*_SAVED
+  int32_t fmt;         // operand format of the MMA: 0 = f16, 1 = bf16, 2 = tf32 (fp32 storage, 32 elements per stage)
   // Operand fetch ahead of use (ops[i].reserved selects the path: 0 = load where the op runs):
   //   vec_slot[j] (reserved = 1 + j): a row vector (bias) - its slice for the tile is staged in
   //     shared memory as fp32 once per tile, while the K loop is still running;

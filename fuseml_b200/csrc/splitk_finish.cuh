@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(256) splitk_finish_kernel(const __grid_constan
       v[4 * i + 3] += x.w;
     }
   }
-  epi::run_program<USES_SAVED, kFinishChunk>(p, m, n0, true, v, nullptr, 0);
+  epi::run_program<USES_SAVED ? epi::kProgGenericSaved : epi::kProgGeneric, kFinishChunk>(p, m, n0, true, v, nullptr, 0);
   if (p.d != nullptr) epi::store_chunk<kFinishChunk>(p.d, m * p.ldd, n0, p.N, p.out_dtype, v);
 }
 

@@ -186,3 +186,32 @@ def test_batched_activations_run_fused_and_match_the_flattened_block(native_lib)
     np.testing.assert_allclose(f(y).reshape(B * S, D), want, **BF16_TOL)
     np.testing.assert_allclose(f(ymax).reshape(-1), want.max(axis=1), **BF16_TOL)
     torch._dynamo.reset()
+
+
+def test_misaligned_views_run_fused_on_an_aligned_copy(native_lib):
+    """A column slice that starts in the middle of a 16-byte word cannot be read by TMA in place.
+    The compile-time layout check sees shapes and strides only, so the launcher meets such a
+    tensor at run time: it copies the operand into an aligned buffer and launches the fused
+    kernel on the copy instead of raising out of the compiled graph."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+
+    torch._dynamo.reset()
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(256, 384).to("cuda", torch.bfloat16)
+    big = torch.randn(200, 264, device="cuda", dtype=torch.bfloat16)
+    aligned, shifted = big[:, 8:264], big[:, 4:260]          # same shape and strides; 16- and 8-byte offsets
+    comp = F.FuseMLCompiler()
+    f = torch.compile(lambda t: torch.nn.functional.gelu(lin(t)), backend=comp)
+    with torch.no_grad():
+        y0 = f(aligned)
+        y1 = f(shifted)
+        ref0 = torch.nn.functional.gelu(lin(aligned).float())
+        ref1 = torch.nn.functional.gelu(lin(shifted).float())
+    torch.cuda.synchronize()
+    assert F.device_status() == 0
+    assert comp.fusion_applied and sum(L.launch_count for L in set(comp.launchers)) == 2
+    np.testing.assert_allclose(y0.float().cpu().numpy(), ref0.cpu().numpy(), **BF16_TOL)
+    np.testing.assert_allclose(y1.float().cpu().numpy(), ref1.cpu().numpy(), **BF16_TOL)
+    torch._dynamo.reset()
