@@ -14,7 +14,7 @@ from pathlib import Path
 
 MAX_EPI_OPS = 16
 MAX_OPERANDS = 8
-ABI_VERSION = 2          # FUSEML_SM100_ABI_VERSION of include/fuseml_sm100.h
+ABI_VERSION = 3          # FUSEML_SM100_ABI_VERSION of include/fuseml_sm100.h
 
 # status codes -----------------------------------------------------------------
 OK = 0
@@ -38,6 +38,7 @@ OP_NAMES = {
 
 # reductions ---------------------------------------------------------------------
 RED_SUM, RED_MAX, RED_MEAN = 1, 2, 4
+PLAN_B_EXPANSION_VALID = 1
 AXIS_M, AXIS_N, AXIS_ALL = 0, 1, 2
 
 
@@ -75,7 +76,7 @@ class Plan(C.Structure):
         ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32),
         ("cluster", C.c_int32), ("acc_stages", C.c_int32), ("grid", C.c_int32), ("group_m", C.c_int32),
         ("smem_bytes", C.c_int32), ("tmem_cols", C.c_int32), ("bound", C.c_int32), ("fuse", C.c_int32),
-        ("split_k", C.c_int32), ("reserved0", C.c_int32),
+        ("split_k", C.c_int32), ("flags", C.c_int32),
         ("flops", C.c_double), ("bytes", C.c_double), ("t_tensor_us", C.c_double),
         ("t_hbm_us", C.c_double), ("t_est_us", C.c_double),
     ]

@@ -81,7 +81,7 @@ def compute_launch_params(M: int, Ncols: int, Kd: int, dtype: torch.dtype = torc
 
 class _Prepared:
     """One (shape, stride) signature: filled descriptor, plan, workspace size, output shapes."""
-    __slots__ = ("desc", "plan", "ws_bytes", "ws", "M", "N", "K", "red_len", "left", "right",
+    __slots__ = ("desc", "plan", "ws_bytes", "ws", "b_tag", "M", "N", "K", "red_len", "left", "right",
                  "views", "out_shape", "aux_shapes", "red_shape")
 
 
@@ -258,6 +258,7 @@ class KernelLauncher:
         if p.ws_bytes < 0:
             raise N.NativeLibraryError("fuseml_sm100_workspace_bytes rejected the descriptor")
         p.ws = {}
+        p.b_tag = {}
         p.views = views if any(v is not None for v in views) else None
         p.out_shape, p.aux_shapes, p.red_shape = self._output_shapes(M, Ncols)
         self._prepared[key] = p
@@ -323,6 +324,15 @@ class KernelLauncher:
                 ws = p.ws[stream] = torch.empty(p.ws_bytes, dtype=torch.uint8, device=device)
             desc.reduce.workspace = ws.data_ptr()
             desc.reduce.workspace_bytes = p.ws_bytes
+            if left.dtype == torch.float32:
+                # fp32 operands are expanded into the workspace before the MMA.  This workspace is
+                # private to (signature, stream): when B is the same storage at the same version
+                # as in the previous launch here (a weight), its expansion is still valid.
+                # (Never while a CUDA graph is being captured: a replay cannot re-check the weight.)
+                tag = (right.data_ptr(), right._version)
+                reuse = p.b_tag.get(stream) == tag and not torch.cuda.is_current_stream_capturing()
+                p.plan.flags = N.PLAN_B_EXPANSION_VALID if reuse else 0
+                p.b_tag[stream] = tag
         if device.index is not None and device.index != torch.cuda.current_device():
             with torch.cuda.device(device):
                 rc = self._lib.fuseml_sm100_gemm_epilogue(C.byref(desc), C.byref(p.plan), C.c_void_p(stream))

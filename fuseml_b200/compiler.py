@@ -13,8 +13,9 @@ What differs from the reference:
 * groups are lowered to a :class:`KernelSpec` and checked for TMA-addressable layouts *before*
   surgery; a group that cannot be expressed is left in the graph as ordinary ATen ops (it was
   never "matched"), instead of failing at the first launch.
-* discovery runs with the DAG / multi-reduction / global-reduction extensions switched on
-  (keyword arguments; the pass itself defaults to the reference's behaviour).
+* discovery runs with the DAG / multi-reduction / global-reduction / bare-trigger extensions
+  switched on (keyword arguments; the pass itself defaults to the reference's behaviour): no
+  ``addmm`` / ``mm`` of a compiled graph is left to a library GEMM.
 * graphs whose tensors live on the CPU are not lowered at all: the fused path has no CPU
   implementation, so the module is handed back unchanged, as the reference does whenever it
   finds nothing to fuse (``:219-228``).
@@ -87,7 +88,7 @@ class FuseMLCompiler:
     """
 
     def __init__(self, registry: SupportedOpsRegistry | None = None, *, dag_epilogue: bool = True,
-                 multi_reduction: bool = True, global_reductions: bool = True) -> None:
+                 multi_reduction: bool = True, global_reductions: bool = True, bare_trigger: bool = True) -> None:
         self.registry: SupportedOpsRegistry = registry or build_default_registry()
         self.fusion_candidates: list = []
         self.fusion_applied: bool = False
@@ -95,7 +96,7 @@ class FuseMLCompiler:
         self.launchers: list[KernelLauncher] = []
         self.declined: list[tuple[str, str]] = []
         self._options = dict(dag_epilogue=dag_epilogue, multi_reduction=multi_reduction,
-                             global_reductions=global_reductions)
+                             global_reductions=global_reductions, bare_trigger=bare_trigger)
         self._generator = Sm100KernelGenerator()
         self._cache = KernelCache()
 

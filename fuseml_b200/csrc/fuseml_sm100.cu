@@ -205,7 +205,7 @@ static int check_plan(const fuseml_plan_t* pl) {
   if (pl->grid <= 0 || pl->group_m <= 0) return FUSEML_E_PLAN;
   if (pl->cluster != 1 && pl->cluster != 2) return FUSEML_E_PLAN;
   if (pl->cluster == 2 && pl->tile_n <= 128) return FUSEML_E_PLAN;
-  if (pl->split_k < 0 || pl->split_k > 64 || pl->reserved0 != 0) return FUSEML_E_PLAN;
+  if (pl->split_k < 0 || pl->split_k > 64 || (pl->flags & ~FUSEML_PLAN_B_EXPANSION_VALID) != 0) return FUSEML_E_PLAN;
   if (pl->split_k > 1 && pl->cluster != 1) return FUSEML_E_PLAN;
   return FUSEML_OK;
 }
@@ -334,8 +334,9 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     const int gb = static_cast<int>(std::min<int64_t>((tb + threads - 1) / threads, 148 * 16));
     split_tf32_kernel<<<ga, threads, 0, stream>>>(reinterpret_cast<const float*>(desc->a), desc->M, desc->K,
                                                   desc->lda, 1, 0, a2, ld);
-    split_tf32_kernel<<<gb, threads, 0, stream>>>(reinterpret_cast<const float*>(desc->b), desc->N, desc->K,
-                                                  desc->b_stride_n, desc->b_stride_k, 1, b2, ld);
+    if ((plan.flags & FUSEML_PLAN_B_EXPANSION_VALID) == 0)
+      split_tf32_kernel<<<gb, threads, 0, stream>>>(reinterpret_cast<const float*>(desc->b), desc->N, desc->K,
+                                                    desc->b_stride_n, desc->b_stride_k, 1, b2, ld);
     if (cudaGetLastError() != cudaSuccess) return FUSEML_E_LAUNCH;
     a_ptr = a2; b_ptr = b2; K = 3 * desc->K; lda = ld; ldb = ld; b_mn = false;
   }

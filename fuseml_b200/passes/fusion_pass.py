@@ -17,7 +17,10 @@ by default so that structural behaviour stays drop-in):
                         is absorbed as a diamond (evaluated with the epilogue's second register);
 * ``multi_reduction``   several reductions of the same tensor become outputs of one kernel; the
                         matrix itself is only written if something else still reads it;
-* ``global_reductions`` whole-tensor ``sum`` / ``amax`` / ``mean`` are accepted as reduction tails.
+* ``global_reductions`` whole-tensor ``sum`` / ``amax`` / ``mean`` are accepted as reduction tails;
+* ``bare_trigger``      an ``addmm`` / ``mm`` that absorbs nothing is still a group (the reference drops
+                        it, fuseml/passes/fusion_pass.py:332-333, and the GEMM then runs in a library):
+                        a bias is an epilogue, and a lone ``mm`` is the same kernel with an empty program.
 """
 from __future__ import annotations
 
@@ -104,12 +107,14 @@ class FuseMLFusionPass:
     _MIN_FUSION_OUTPUT_ELEMENTS: int = 500_000
 
     def __init__(self, graph_module: torch.fx.GraphModule, registry: SupportedOpsRegistry | None = None, *,
-                 dag_epilogue: bool = False, multi_reduction: bool = False, global_reductions: bool = False) -> None:
+                 dag_epilogue: bool = False, multi_reduction: bool = False, global_reductions: bool = False,
+                 bare_trigger: bool = False) -> None:
         self.graph_module = graph_module
         self.registry = registry or build_default_registry()
         self.dag_epilogue = dag_epilogue
         self.multi_reduction = multi_reduction
         self.global_reductions = global_reductions
+        self.bare_trigger = bare_trigger
 
     # ------------------------------------------------------------------ discovery
     def _find_fusion_groups(self) -> list[FusionGroup]:
@@ -120,7 +125,7 @@ class FuseMLFusionPass:
                 continue
             group = self._grow_group(node, claimed)
             self._resolve_get_attr_bindings(group)
-            if len(group) > 1:
+            if len(group) > 1 or self.bare_trigger:
                 group.output_metadata = self._extract_tensor_metadata(group.output_node)
                 group.original_inputs = list(group.inputs)
                 for n in group.all_nodes:

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define FUSEML_SM100_ABI_VERSION 2
+#define FUSEML_SM100_ABI_VERSION 3
 
 /* ---- status codes ------------------------------------------------------ */
 enum {
@@ -158,6 +158,13 @@ typedef struct {
 } fuseml_gemm_desc_t;
 
 /* ---- plan: what the roofline router decides ----------------------------- */
+/* plan.flags bit: fp32 operands are expanded into the workspace before the MMA (see
+ * fuseml_sm100_workspace_bytes).  A caller that launches the same descriptor again with the
+ * same workspace and an unchanged B (a weight) may set this bit: the expansion of B found in
+ * the workspace is reused and only A is expanded.  The caller vouches that neither B nor that
+ * part of the workspace was written in between.                                            */
+#define FUSEML_PLAN_B_EXPANSION_VALID 1
+
 typedef struct {
   int32_t tile_m;        /* 128                                              */
   int32_t tile_n;        /* 64 | 128 | 256                                   */
@@ -174,7 +181,7 @@ typedef struct {
   int32_t split_k;       /* CTAs sharing one tile's K loop (1 = no split);   */
                          /* > 1: fp32 partial tiles in the workspace, folded */
                          /* and run through the epilogue by a second kernel  */
-  int32_t reserved0;     /* keeps the doubles 8-byte aligned; must be 0      */
+  int32_t flags;         /* FUSEML_PLAN_* bits, 0 from fuseml_sm100_plan     */
   double flops;          /* 2*M*N*K                                          */
   double bytes;          /* algorithmic HBM bytes                            */
   double t_tensor_us;    /* flops / tensor peak                              */

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 BF16_TOL = dict(rtol=1.6e-2, atol=1e-2)
 F32_TOL = dict(rtol=1e-3, atol=1e-3)
-EXPECTED_KERNELS = {"cfg1": 1, "cfg2": 1, "cfg3": 1, "cfg4": 2, "cfg5": 8}
+EXPECTED_KERNELS = {"cfg1": 2, "cfg2": 1, "cfg3": 1, "cfg4": 2, "cfg5": 8}
 
 
 def _cuda_case(name):
@@ -214,4 +214,31 @@ def test_misaligned_views_run_fused_on_an_aligned_copy(native_lib):
     assert comp.fusion_applied and sum(L.launch_count for L in set(comp.launchers)) == 2
     np.testing.assert_allclose(y0.float().cpu().numpy(), ref0.cpu().numpy(), **BF16_TOL)
     np.testing.assert_allclose(y1.float().cpu().numpy(), ref1.cpu().numpy(), **BF16_TOL)
+    torch._dynamo.reset()
+
+
+def test_fp32_weight_expansion_is_reused_until_the_weight_changes(native_lib):
+    """fp32 operands are expanded into the launcher's workspace before the MMA; the expansion of
+    an unchanged weight is reused by the next launch, and redone after an in-place update."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+
+    torch._dynamo.reset()
+    torch.manual_seed(5)
+    lin = torch.nn.Linear(96, 160).to("cuda")
+    x = torch.randn(64, 96, device="cuda")
+    comp = F.FuseMLCompiler()
+    f = torch.compile(lambda t: torch.relu(lin(t)), backend=comp)
+    with torch.no_grad():
+        y0 = f(x)
+        y1 = f(x)                                  # second launch: B's expansion reused
+        assert torch.equal(y0, y1)
+        lin.weight.mul_(-1.0)                      # in-place update bumps the version counter
+        y2 = f(x)
+        ref = torch.relu(lin(x))
+    torch.cuda.synchronize()
+    assert F.device_status() == 0
+    np.testing.assert_allclose(y2.cpu().numpy(), ref.cpu().numpy(), **F32_TOL)
+    assert not torch.equal(y2, y0)
     torch._dynamo.reset()
