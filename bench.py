@@ -370,8 +370,8 @@ class SmallFp32MLP(Workload):
         self.algo_bytes = 4.0 * (rows * d_model + 2 * d_model * d_inter + d_inter + d_model + rows * d_model) \
             + 8.0 * rows * d_inter
         self.expected_kernels = 2
-        # per Linear: two operand expansions, the split-K GEMM and its finish pass
-        self.launches_per_step = 8
+        # per Linear: the operand expansion, the split-K GEMM and its finish pass
+        self.launches_per_step = 6
         self.gemm_launches_per_step = 2
         self.h2d_bytes = rows * d_model * 4
         self.d2h_bytes = rows * d_model * 4

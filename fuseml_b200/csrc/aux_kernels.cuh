@@ -166,21 +166,33 @@ __global__ void reduce_cols_kernel(const void* __restrict__ x, int32_t dtype, in
 // where hi keeps the top 10 mantissa bits (exactly a TF32 value) and lo = x - hi.
 // A TF32 GEMM over the 3K-long rows then computes hi*hi + lo*hi + hi*lo, i.e. the
 // fp32 product to ~2^-21 relative, with fp32 accumulation.
-__global__ void split_tf32_kernel(const float* __restrict__ src, int64_t rows, int64_t K, int64_t stride_r,
-                                  int64_t stride_k, int32_t variant, float* __restrict__ dst, int64_t ld) {
-  const int64_t total = rows * K;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+struct SplitJob {
+  const float* src;
+  int64_t rows, K, stride_r, stride_k;
+  int32_t variant;     // 0: [hi|lo|hi] (the A side), 1: [hi|hi|lo] (the B side)
+  float* dst;
+  int64_t ld;
+  int32_t blocks;      // blocks of the launch that work on this job (0 = none)
+};
+
+// Both operands in one launch: blocks [0, a.blocks) expand A, the rest expand B.
+__global__ void split_tf32_kernel(const SplitJob a, const SplitJob b) {
+  const bool first = static_cast<int32_t>(blockIdx.x) < a.blocks;
+  const SplitJob& j = first ? a : b;
+  const int64_t block = first ? blockIdx.x : blockIdx.x - a.blocks;
+  const int64_t total = j.rows * j.K;
+  for (int64_t i = block * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(j.blocks) * blockDim.x) {
     // when K is the strided dimension of the source, walk rows fastest so that reads coalesce
     int64_t r, k;
-    if (stride_k == 1) { r = i / K; k = i - r * K; } else { k = i / rows; r = i - k * rows; }
-    const float x = src[r * stride_r + k * stride_k];
+    if (j.stride_k == 1) { r = i / j.K; k = i - r * j.K; } else { k = i / j.rows; r = i - k * j.rows; }
+    const float x = j.src[r * j.stride_r + k * j.stride_k];
     const float hi = __uint_as_float(__float_as_uint(x) & 0xffffe000u);
     const float lo = x - hi;
-    float* o = dst + r * ld;
+    float* o = j.dst + r * j.ld;
     o[k] = hi;
-    o[K + k] = variant == 0 ? lo : hi;
-    o[2 * K + k] = variant == 0 ? hi : lo;
+    o[j.K + k] = j.variant == 0 ? lo : hi;
+    o[2 * j.K + k] = j.variant == 0 ? hi : lo;
   }
 }
 

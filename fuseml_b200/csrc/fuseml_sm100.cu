@@ -330,13 +330,13 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     float* b2 = reinterpret_cast<float*>(ws + w.split_b_off);
     const int threads = 256;
     const int64_t ta = desc->M * desc->K, tb = desc->N * desc->K;
-    const int ga = static_cast<int>(std::min<int64_t>((ta + threads - 1) / threads, 148 * 16));
-    const int gb = static_cast<int>(std::min<int64_t>((tb + threads - 1) / threads, 148 * 16));
-    split_tf32_kernel<<<ga, threads, 0, stream>>>(reinterpret_cast<const float*>(desc->a), desc->M, desc->K,
-                                                  desc->lda, 1, 0, a2, ld);
-    if ((plan.flags & FUSEML_PLAN_B_EXPANSION_VALID) == 0)
-      split_tf32_kernel<<<gb, threads, 0, stream>>>(reinterpret_cast<const float*>(desc->b), desc->N, desc->K,
-                                                    desc->b_stride_n, desc->b_stride_k, 1, b2, ld);
+    SplitJob ja = {reinterpret_cast<const float*>(desc->a), desc->M, desc->K, desc->lda, 1, 0, a2, ld,
+                   static_cast<int32_t>(std::min<int64_t>((ta + threads - 1) / threads, 148 * 8))};
+    SplitJob jb = {reinterpret_cast<const float*>(desc->b), desc->N, desc->K, desc->b_stride_n, desc->b_stride_k, 1, b2, ld,
+                   static_cast<int32_t>(std::min<int64_t>((tb + threads - 1) / threads, 148 * 8))};
+    if (plan.flags & FUSEML_PLAN_B_EXPANSION_VALID) jb.blocks = 0;
+    // one launch for both operands
+    split_tf32_kernel<<<ja.blocks + jb.blocks, threads, 0, stream>>>(ja, jb);
     if (cudaGetLastError() != cudaSuccess) return FUSEML_E_LAUNCH;
     a_ptr = a2; b_ptr = b2; K = 3 * desc->K; lda = ld; ldb = ld; b_mn = false;
   }
