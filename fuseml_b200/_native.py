@@ -39,6 +39,7 @@ OP_NAMES = {
 # reductions ---------------------------------------------------------------------
 RED_SUM, RED_MAX, RED_MEAN = 1, 2, 4
 PLAN_B_EXPANSION_VALID = 1
+WHERE_MMA_FULL = 0x202
 AXIS_M, AXIS_N, AXIS_ALL = 0, 1, 2
 
 
@@ -99,6 +100,7 @@ EXPORTS = (
     "fuseml_sm100_gemm_epilogue", "fuseml_sm100_reduce_tail", "fuseml_sm100_device_status",
     "fuseml_sm100_strerror", "fuseml_sm100_abi_version",
     "fuseml_sm100_gemm_epilogue_noalloc", "fuseml_sm100_noalloc_scratch_bytes",
+    "fuseml_sm100_set_diagnostics",
 )
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfuseml_sm100.so"
@@ -133,6 +135,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.fuseml_sm100_reduce_tail.restype = C.c_int
     lib.fuseml_sm100_reduce_tail.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                              C.POINTER(Reduce), C.c_void_p]
+    lib.fuseml_sm100_set_diagnostics.restype = C.c_int
+    lib.fuseml_sm100_set_diagnostics.argtypes = [C.c_int64, C.c_int32]
     lib.fuseml_sm100_device_status.restype = C.c_int
     lib.fuseml_sm100_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
 

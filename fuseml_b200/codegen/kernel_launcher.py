@@ -79,9 +79,24 @@ def compute_launch_params(M: int, Ncols: int, Kd: int, dtype: torch.dtype = torc
     return LaunchParams(plan.tile_m, plan.tile_n, plan.tile_k, plan.group_m, 6, plan.stages)
 
 
+_BUILD_ID: list = []
+
+
+def _build_id() -> str:
+    """Short digest of the sources the loaded library was built from (part of every plan-cache key)."""
+    if not _BUILD_ID:
+        from ..build import source_digest
+
+        try:
+            _BUILD_ID.append(source_digest()[:12])
+        except OSError:
+            _BUILD_ID.append("unknown")
+    return _BUILD_ID[0]
+
+
 class _Prepared:
     """One (shape, stride) signature: filled descriptor, plan, workspace size, output shapes."""
-    __slots__ = ("desc", "plan", "ws_bytes", "ws", "b_tag", "M", "N", "K", "red_len", "left", "right",
+    __slots__ = ("desc", "plan", "ws_bytes", "ws", "b_tag", "tune_key", "M", "N", "K", "red_len", "left", "right",
                  "views", "out_shape", "aux_shapes", "red_shape")
 
 
@@ -97,7 +112,7 @@ class KernelLauncher:
                  reduction_op: str | None = None, reduction_axis: int | None = None,
                  eager_fn: Callable | None = None, is_autotuned: bool = False, sram_autotuner: Any = None,
                  mean_epilogue_fused: bool = True, reduction_dtypes: Sequence[torch.dtype] | None = None,
-                 reduction_shape: Sequence[int] | None = None) -> None:
+                 reduction_shape: Sequence[int] | None = None, plan_cache: Any = None, autotune: bool = False) -> None:
         self.__name__ = "fuseml_fused_kernel"
         if not isinstance(kernel_fn, KernelSpec):
             raise TypeError("kernel_fn must be a KernelSpec (the lowered form of a FusionGroup)")
@@ -133,6 +148,11 @@ class KernelLauncher:
         self._sram_autotuner = sram_autotuner
         self._skip_stride_check = all(all(s >= 0 for s in d.stride) for d in self._input_descriptors)
         self._prepared: dict[tuple, _Prepared] = {}
+        # measured plans (codegen/plan_cache.py): looked up per signature, filled by timing a few
+        # candidate plans on the first call when `autotune` is set
+        self._plan_cache = plan_cache
+        self._autotune = bool(autotune)
+        self.tuned_signatures = 0
         self._lib = None
         self.launch_count = 0
         # operand slots of the program: input indices in order of first use
@@ -254,6 +274,17 @@ class KernelLauncher:
                 p.plan.tile_n = self._launch_params.block_n
                 tiles = ((M + 127) // 128) * ((Ncols + p.plan.tile_n - 1) // p.plan.tile_n)
                 p.plan.grid = max(1, min(p.plan.grid if p.plan.grid > 0 else tiles, tiles))
+        p.tune_key = None
+        if self._plan_cache is not None:
+            from .plan_cache import apply_entry, plan_key
+
+            key_str = plan_key(torch.cuda.get_device_name(left.device), _build_id(), M, Ncols, Kd, p.desc.ab_dtype,
+                               p.desc.out_dtype, "k" if right.stride(0) == 1 else "n",
+                               spec.signature()[:16] + ":" + ",".join(f"{o.stride_m and 1}{o.stride_n and 1}{o.dtype}"
+                                                                       for o in p.desc.operands[:p.desc.n_operands]))
+            entry = self._plan_cache.get(key_str)
+            if entry is None or not apply_entry(p.plan, entry):
+                p.tune_key = key_str if self._autotune else None
         p.ws_bytes = int(self._lib.fuseml_sm100_workspace_bytes(C.byref(p.desc), C.byref(p.plan)))
         if p.ws_bytes < 0:
             raise N.NativeLibraryError("fuseml_sm100_workspace_bytes rejected the descriptor")
@@ -333,6 +364,8 @@ class KernelLauncher:
                 reuse = p.b_tag.get(stream) == tag and not torch.cuda.is_current_stream_capturing()
                 p.plan.flags = N.PLAN_B_EXPANSION_VALID if reuse else 0
                 p.b_tag[stream] = tag
+        if p.tune_key is not None and not torch.cuda.is_current_stream_capturing():
+            self._tune(p, desc, device, stream)
         if device.index is not None and device.index != torch.cuda.current_device():
             with torch.cuda.device(device):
                 rc = self._lib.fuseml_sm100_gemm_epilogue(C.byref(desc), C.byref(p.plan), C.c_void_p(stream))
@@ -359,6 +392,39 @@ class KernelLauncher:
             return (red_out[0], *aux_out, *red_out[1:])
         outputs.extend(red_out)
         return outputs[0] if len(outputs) == 1 else tuple(outputs)
+
+    def _tune(self, p: _Prepared, desc, device, stream) -> None:
+        """First call of a signature with autotuning on: time the router's plan and its neighbours on
+        the live tensors (the descriptor is complete at this point), keep the fastest, persist it."""
+        from .plan_cache import candidate_plans, entry_of, tune_plan
+
+        key, p.tune_key = p.tune_key, None
+        cands = candidate_plans(p.plan, p.M, p.N, K.device_props(device).sm_count, bool(self._reductions))
+        sizes = [int(self._lib.fuseml_sm100_workspace_bytes(C.byref(desc), C.byref(c))) for c in cands]
+        cands = [c for c, n in zip(cands, sizes) if n >= 0]
+        need = max([n for n in sizes if n >= 0] + [0])
+        saved_ws = (desc.reduce.workspace, desc.reduce.workspace_bytes)
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=device)
+        desc.reduce.workspace, desc.reduce.workspace_bytes = scratch.data_ptr(), need
+
+        def launch(plan) -> None:
+            with torch.cuda.device(device):
+                N.check(self._lib.fuseml_sm100_gemm_epilogue(C.byref(desc), C.byref(plan), C.c_void_p(stream)), "tuning launch")
+
+        best, us, tried = tune_plan(launch, cands)
+        desc.reduce.workspace, desc.reduce.workspace_bytes = saved_ws
+        if best is None:
+            return
+        p.plan = best
+        p.ws_bytes = int(self._lib.fuseml_sm100_workspace_bytes(C.byref(desc), C.byref(best)))
+        p.ws, p.b_tag = {}, {}
+        if p.ws_bytes:
+            ws = p.ws[stream] = torch.empty(p.ws_bytes, dtype=torch.uint8, device=device)
+            desc.reduce.workspace, desc.reduce.workspace_bytes = ws.data_ptr(), p.ws_bytes
+        self.tuned_signatures += 1
+        self._plan_cache.put(key, entry_of(best, us, tried))
+        logger.info("tuned M=%d N=%d K=%d: tile_n=%d cluster=%d group_m=%d split_k=%d, %.1f us (%d candidates)",
+                    p.M, p.N, p.K, best.tile_n, best.cluster, best.group_m, best.split_k, us, tried)
 
     def __repr__(self) -> str:
         ins = [d.name for d in self._input_descriptors]

@@ -22,6 +22,7 @@ What differs from the reference:
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Callable
 
 import torch
@@ -88,7 +89,8 @@ class FuseMLCompiler:
     """
 
     def __init__(self, registry: SupportedOpsRegistry | None = None, *, dag_epilogue: bool = True,
-                 multi_reduction: bool = True, global_reductions: bool = True, bare_trigger: bool = True) -> None:
+                 multi_reduction: bool = True, global_reductions: bool = True, bare_trigger: bool = True,
+                 plan_cache: Any = None, autotune: bool | None = None) -> None:
         self.registry: SupportedOpsRegistry = registry or build_default_registry()
         self.fusion_candidates: list = []
         self.fusion_applied: bool = False
@@ -99,6 +101,22 @@ class FuseMLCompiler:
                              global_reductions=global_reductions, bare_trigger=bare_trigger)
         self._generator = Sm100KernelGenerator()
         self._cache = KernelCache()
+        # Measured launch plans on disk (codegen/plan_cache.py).  `plan_cache` is a PlanCache, a
+        # path, or None: then the file named by FUSEML_PLAN_CACHE (or the default under ~/.cache)
+        # is used when that variable is set or autotuning is on.  `autotune` (default: the
+        # FUSEML_AUTOTUNE environment variable) times candidate plans on the first call of every
+        # new shape and stores the winner there.
+        from .codegen import plan_cache as _pc
+
+        self.autotune = _pc.autotune_requested() if autotune is None else bool(autotune)
+        if isinstance(plan_cache, _pc.PlanCache):
+            self.plan_cache = plan_cache
+        elif plan_cache is not None:
+            self.plan_cache = _pc.PlanCache(plan_cache)
+        elif self.autotune or os.environ.get(_pc.ENV_PATH):
+            self.plan_cache = _pc.PlanCache()
+        else:
+            self.plan_cache = None
 
     # ------------------------------------------------------------------ torch.compile entry
     def __call__(self, gm: torch.fx.GraphModule, example_inputs: list) -> Callable:
@@ -252,7 +270,8 @@ class FuseMLCompiler:
                 return hit
         launcher = KernelLauncher(
             spec, descs, out_desc, inter, descs[spec.left_index].name, descs[spec.right_index].name,
-            is_autotuned=True, reduction_dtypes=red_dtypes, reduction_shape=red_shape)
+            is_autotuned=True, reduction_dtypes=red_dtypes, reduction_shape=red_shape,
+            plan_cache=self.plan_cache, autotune=self.autotune)
         if key is not None:
             self._cache.store(key, launcher)
         self.launchers.append(launcher)

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -19,6 +20,10 @@ namespace fuseml {
 
 // Status word written by bounded waits that ran out (0 = none did).
 __device__ int32_t g_status_word = 0;
+
+// Diagnostics copied into every launch's parameters (fuseml_sm100_set_diagnostics).
+static std::atomic<uint32_t> g_diag_wait_limit_us{0};
+static std::atomic<int32_t> g_diag_drop_last_load{0};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -418,6 +423,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   void* status_ptr = nullptr;
   if (cudaGetSymbolAddress(&status_ptr, g_status_word) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
   p.status = reinterpret_cast<int32_t*>(status_ptr);
+  p.wait_limit_us = g_diag_wait_limit_us.load(std::memory_order_relaxed);
+  p.drop_last_load = g_diag_drop_last_load.load(std::memory_order_relaxed);
 
   if (plan.split_k > 1) {
     // Split-K: every CTA runs one K slice of one tile and stores its raw fp32 accumulator; the
@@ -626,6 +633,13 @@ int fuseml_sm100_gemm_epilogue_noalloc(const fuseml_gemm_desc_t* desc, const fus
   local.reduce.workspace = scratch;
   local.reduce.workspace_bytes = kNoAllocScratchBytes;
   return fuseml_sm100_gemm_epilogue(&local, &plan, cuda_stream);
+}
+
+int fuseml_sm100_set_diagnostics(int64_t wait_limit_us, int32_t drop_last_load) {
+  if (wait_limit_us < 0 || wait_limit_us > 0xffffffffll) return FUSEML_E_LIMIT;
+  g_diag_wait_limit_us.store(static_cast<uint32_t>(wait_limit_us), std::memory_order_relaxed);
+  g_diag_drop_last_load.store(drop_last_load ? 1 : 0, std::memory_order_relaxed);
+  return FUSEML_OK;
 }
 
 int fuseml_sm100_device_status(void* cuda_stream, int32_t* status_out) {

@@ -196,7 +196,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
     ptx::mbar_init(tile_in_bar, 1);
     for (int j = 0; j < 4; ++j) ptx::mbar_init(box_bar(j), kEpiWarps);
-    *abort_flag = 0u;
+    abort_flag[0] = 0u;
+    abort_flag[1] = p.wait_limit_us;
     ptx::fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -267,6 +268,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             break;
           }
           FUSEML_STALL_ADD(st_empty);
+          // host-injected failure (diagnostics): the last K block of the last tile is never
+          // loaded and its barrier never armed; nothing is in flight when the MMA thread gives up
+          if (p.drop_last_load && kb == kb_end - 1 && t + tile_step >= p.num_tiles) break;
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
           const uint32_t b_dst = a_dst + L::kABytes;
           // one load helper for both modes: completion bytes go to `bar` (for a pair: the
@@ -342,7 +346,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const int32_t row0 = (tm * CG + static_cast<int32_t>(cta_rank)) * kTileM;
         const int32_t n_tile0 = tn * bn;
         for (int j = 0; j < tile_boxes; ++j) {
-          if (!ptx::mbar_wait(box_bar(j), 0u, abort_flag, p.status, kWhereStoreBox, true)) {
+          // (after a failed wait elsewhere the epilogue warps still arrive, without having
+          // written anything: store nothing then)
+          if (!ptx::mbar_wait(box_bar(j), 0u, abort_flag, p.status, kWhereStoreBox, true) || *abort_flag) {
             ok = false;
             break;
           }

@@ -65,6 +65,12 @@ struct GemmParams {
   int32_t kb_per_split;
   float* split_ws;
   int32_t* status;     // device status word (bounded-wait time-outs)
+  // Diagnostics (fuseml_sm100_set_diagnostics; both 0 in normal operation): the wall-clock limit
+  // of a bounded wait in microseconds (0 = the built-in two seconds), and a host-injected
+  // failure: the producer issues no load for the last K block of its last tile, so that the MMA
+  // thread waits on a barrier that nothing completes while no copy is in flight.
+  uint32_t wait_limit_us;
+  int32_t drop_last_load;
 };
 
 // Tile id -> (tile row, tile column).  Tiles are walked in groups of

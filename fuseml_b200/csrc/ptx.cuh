@@ -84,7 +84,9 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by every
 // role of the CTA: the first waiter to run out of time sets it and records
 // `where` in the global status word; everyone else sees the flag at their next
-// poll and returns false as well.
+// poll and returns false as well.  The word after the flag holds the limit in
+// microseconds when a caller shortened it (0 = kWaitLimitNs); it is read on the
+// slow path only.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           int32_t* status_word, int32_t where, bool backoff = false) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -97,7 +99,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (backoff) __nanosleep(it < 64 ? 64 : 256);
     if ((it & 0xFF) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      // A wait with back-off is a wait for another role's whole K loop (the epilogue waiting for
+      // an accumulator): it gets twice the limit, so that the role next to the cause (the MMA
+      // thread missing its operands, the producer missing a free stage) is the one that reports.
+      const uint32_t limit_us = abort_flag[1];
+      const uint64_t limit_ns = (limit_us ? static_cast<uint64_t>(limit_us) * 1000ull : kWaitLimitNs) << (backoff ? 1 : 0);
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1u;
         if (status_word) atomicCAS(status_word, 0, where);
         return false;

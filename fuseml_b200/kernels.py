@@ -322,3 +322,10 @@ def device_status() -> int:
     stream = torch.cuda.current_stream().cuda_stream
     N.load().fuseml_sm100_device_status(C.c_void_p(stream), C.byref(out))
     return int(out.value)
+
+
+def set_diagnostics(wait_limit_us: int = 0, drop_last_load: bool = False) -> None:
+    """Shorten the device-side wait limit and / or inject a lost operand load into the launches
+    that follow (``fuseml_sm100_set_diagnostics``); ``set_diagnostics()`` restores normal operation."""
+    N.check(N.load().fuseml_sm100_set_diagnostics(int(wait_limit_us), 1 if drop_last_load else 0),
+            "fuseml_sm100_set_diagnostics")

@@ -256,6 +256,28 @@ int64_t fuseml_sm100_noalloc_scratch_bytes(void);
 int fuseml_sm100_reduce_tail(const void* x, int32_t dtype, int64_t M, int64_t N, int64_t ldx,
                              const fuseml_reduce_t* reduce, void* cuda_stream);
 
+/* No counterpart in the reference.  Diagnostics for the bounded device-side waits, applied to
+ * every launch made afterwards by this process (0, 0 restores normal operation):
+ *   wait_limit_us   wall-clock limit of one wait in microseconds (0 = the built-in 2 s);
+ *   drop_last_load  host-injected failure: each CTA's producer issues no TMA load for the last
+ *                   K block of its last tile.  The MMA thread then waits on a barrier that nothing
+ *                   completes, with no copy in flight, until the limit runs out; the kernel
+ *                   records where it gave up, frees its TMEM and returns; the output is undefined
+ *                   and fuseml_sm100_device_status reports FUSEML_E_TIMEOUT.
+ * Used by the tests of the time-out path; nothing on the GPU faults or traps. */
+int fuseml_sm100_set_diagnostics(int64_t wait_limit_us, int32_t drop_last_load);
+
+/* Where a bounded wait gave up (the value fuseml_sm100_device_status returns in *status_out). */
+enum {
+  FUSEML_WHERE_PRODUCER_EMPTY = 0x201,   /* TMA producer: a ring stage never became free      */
+  FUSEML_WHERE_MMA_FULL = 0x202,         /* MMA thread: operands of a K block never arrived   */
+  FUSEML_WHERE_MMA_TMEM_EMPTY = 0x203,   /* MMA thread: no accumulator buffer was handed back */
+  FUSEML_WHERE_EPILOGUE_TMEM_FULL = 0x204,
+  FUSEML_WHERE_PRODUCER_DRAIN = 0x205,
+  FUSEML_WHERE_EPILOGUE_TILE_IN = 0x206,
+  FUSEML_WHERE_STORE_BOX = 0x207
+};
+
 /* Reads and clears the device-side status word written by bounded waits.
  * Synchronises the given stream.  0 = no kernel gave up. */
 int fuseml_sm100_device_status(void* cuda_stream, int32_t* status_out);

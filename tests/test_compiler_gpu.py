@@ -242,3 +242,66 @@ def test_fp32_weight_expansion_is_reused_until_the_weight_changes(native_lib):
     np.testing.assert_allclose(y2.cpu().numpy(), ref.cpu().numpy(), **F32_TOL)
     assert not torch.equal(y2, y0)
     torch._dynamo.reset()
+
+
+def test_autotuned_plan_is_persisted_and_reused(native_lib, tmp_path):
+    """With autotuning on, the first call of a shape times the router's plan and its neighbours
+    and writes the winner to the plan cache; a second compiler (a later process) pointed at the
+    same file starts from that plan without measuring, and computes the same matrix."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+
+    torch.manual_seed(7)
+    lin = torch.nn.Linear(512, 2048).to("cuda", torch.bfloat16)
+    x = torch.randn(1024, 512, device="cuda", dtype=torch.bfloat16)
+    path = tmp_path / "plans.json"
+    outs = []
+    for autotune in (True, False):
+        torch._dynamo.reset()
+        comp = F.FuseMLCompiler(plan_cache=path, autotune=autotune)
+        f = torch.compile(lambda t: torch.nn.functional.gelu(lin(t)), backend=comp)
+        with torch.no_grad():
+            outs.append(f(x))
+        torch.cuda.synchronize()
+        assert F.device_status() == 0
+        (launcher,) = set(comp.launchers)
+        if autotune:
+            assert launcher.tuned_signatures == 1 and path.exists() and len(comp.plan_cache) == 1
+        else:
+            assert launcher.tuned_signatures == 0 and comp.plan_cache.hits == 1
+    with torch.no_grad():
+        ref = torch.nn.functional.gelu(lin(x).float())
+    np.testing.assert_allclose(outs[0].float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
+    assert torch.equal(outs[0], outs[1])
+    torch._dynamo.reset()
+
+
+def test_compiled_forward_replays_from_a_cuda_graph(native_lib):
+    """The launch path allocates through torch only and never synchronises the host, so a compiled
+    forward can be captured once and replayed (the reference's launcher was built towards the same
+    use, fuseml/codegen/kernel_launcher.py:640-670): new input values written into the static
+    input tensor show up in the replayed output."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+    from fuseml_b200.runtime import GraphedCallable
+
+    torch._dynamo.reset()
+    case, module, args = _cuda_case("cfg4")
+    comp = F.FuseMLCompiler()
+    compiled = torch.compile(module, backend=comp)
+    static_x = args[0].clone()
+    graphed = GraphedCallable(compiled, static_x)
+    before = sum(L.launch_count for L in set(comp.launchers))
+    y0 = graphed().clone()
+    new_x = torch.randn_like(static_x)
+    static_x.copy_(new_x)
+    y1 = graphed().clone()
+    torch.cuda.synchronize()
+    assert F.device_status() == 0
+    assert sum(L.launch_count for L in set(comp.launchers)) == before, "replays do not pass through Python"
+    with torch.no_grad():
+        ref0, ref1 = compiled(args[0]), compiled(new_x)
+    assert torch.equal(y0, ref0) and torch.equal(y1, ref1) and not torch.equal(y0, y1)
+    torch._dynamo.reset()

@@ -267,3 +267,37 @@ def test_row_grouping_helpers():
     assert c((512, 256), rows, n) is None            # broadcast over the batch only: not a [rows, N] pattern
     assert c((4, 1, 256), rows, n) is None
     assert c((256,), 256, 256) == "row"              # the reference's 1-D rule: length N runs along N first
+
+
+def test_plan_cache_round_trip_and_candidates(tmp_path):
+    """Measured plans persist as JSON: written atomically, merged on write, malformed entries
+    ignored; the candidate list holds the router's plan first and only neighbours that differ."""
+    from fuseml_b200.codegen import plan_cache as pc
+
+    path = tmp_path / "sub" / "plans.json"
+    cache = pc.PlanCache(path)
+    assert len(cache) == 0 and cache.get("missing") is None and cache.misses == 1
+    plan = N.Plan()
+    plan.tile_m, plan.tile_n, plan.cluster, plan.grid, plan.group_m, plan.split_k = 128, 224, 2, 148, 4, 1
+    key = pc.plan_key("NVIDIA B200", "abc123", 1024, 16384, 4096, N.BF16, N.BF16, "k", "sig")
+    cache.put(key, pc.entry_of(plan, 61.25, 5))
+    other = pc.PlanCache(path)                       # a second process
+    other.put("other-key", pc.entry_of(plan, 1.0, 1))
+    again = pc.PlanCache(path)
+    assert len(again) == 2 and again.get(key)["tile_n"] == 224 and again.get(key)["us"] == 61.25
+    fresh = N.Plan()
+    assert pc.apply_entry(fresh, again.get(key)) and (fresh.tile_n, fresh.cluster, fresh.grid) == (224, 2, 148)
+    for bad in ({}, {"tile_n": 48, "cluster": 2, "grid": 1, "group_m": 1, "split_k": 1},
+                {"tile_n": 256, "cluster": 3, "grid": 1, "group_m": 1, "split_k": 1}):
+        untouched = N.Plan()
+        assert not pc.apply_entry(untouched, bad) and untouched.tile_n == 0
+    path.write_text("not json")
+    assert len(pc.PlanCache(path)) == 0              # unreadable file: ignored, not fatal
+    base = N.Plan()
+    base.tile_m, base.tile_n, base.cluster, base.grid, base.group_m, base.split_k = 128, 256, 2, 148, 4, 1
+    # 1024 rows x 16384 columns: 256 tiles are 3.46 waves of 74 pairs; 224-wide tiles fill four waves
+    shard = pc.candidate_plans(base, 1024, 16384)
+    assert shard[0].tile_n == 256 and 224 in [c.tile_n for c in shard]
+    # 8192 rows: 27.7 waves, nothing to gain from narrower tiles; only the group size varies
+    full = pc.candidate_plans(base, 8192, 16384)
+    assert {c.tile_n for c in full} == {256} and len(full) == 3

@@ -591,3 +591,49 @@ def test_full_size_cfg5_matches_oracle_on_sampled_rows_and_its_own_fold(K):
     assert abs(float(got["sum"]) - fold_sum) <= 1e-3 * abs(fold_sum) + rounding, (float(got["sum"]), fold_sum, rounding)
     top = float(y.max())
     assert abs(float(got["amax"]) - top) <= 2.0 ** -8 * abs(top), (float(got["amax"]), top)
+
+
+# ---- the time-out path ----------------------------------------------------------------------
+
+@pytest.mark.parametrize("cluster", [1, 2])
+def test_a_wait_that_runs_out_is_reported_and_the_next_launch_is_correct(K, cluster):
+    """Every device-side wait is bounded.  The failure is injected on the host: with the
+    diagnostic switch on, each producer issues no TMA load for the last K block of its last tile,
+    so the MMA thread waits (20 ms here instead of 2 s) on a barrier that nothing completes, with
+    no copy in flight.  The kernel records where it gave up, frees its TMEM and returns; the host
+    reads FUSEML_E_TIMEOUT / WHERE_MMA_FULL, and the same launch without the switch is correct."""
+    import ctypes as C
+
+    from fuseml_b200 import _native as N
+
+    lib = N.load()
+    g = torch.Generator().manual_seed(21)
+    M = 128 if cluster == 1 else 256
+    a = torch.randn(M, 256, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(512, 256, generator=g) / 16).to(torch.bfloat16).cuda()
+
+    def launch():
+        out = torch.empty(M, 512, dtype=torch.bfloat16, device="cuda")
+        desc = N.GemmDesc()
+        K.fill_desc(desc, a, w.t(), None, out, torch.bfloat16)
+        plan = K.plan_for(desc, K.device_props())
+        # two 256-column tiles walked by one CTA (or one CTA pair): the persistent eight-warp instance
+        plan.tile_n, plan.cluster, plan.split_k, plan.grid = 256, cluster, 1, cluster
+        return K.fused_gemm(a, w.t(), None, out=out, plan=plan)
+
+    good = launch()
+    torch.cuda.synchronize()
+    _status_ok(K)
+    K.set_diagnostics(wait_limit_us=20000, drop_last_load=True)
+    try:
+        launch()
+        status = C.c_int32(0)
+        rc = lib.fuseml_sm100_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(status))
+    finally:
+        K.set_diagnostics()
+    assert rc == N.E_TIMEOUT and status.value == N.WHERE_MMA_FULL, (rc, hex(status.value))
+    again = launch()
+    torch.cuda.synchronize()
+    _status_ok(K)
+    assert torch.equal(again, good)
+    np.testing.assert_allclose(good.float().cpu().numpy(), (a.float() @ w.float().t()).cpu().numpy(), **BF16_TOL)
