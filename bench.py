@@ -46,10 +46,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum),
 # from the ncu captures summarised under profiles/gemm_epilogue_kernel_v2_*.md.  cfg4 is the
-# mean of its two launches (GEMM1 0.670 GB, GEMM2 1.751 GB: with K = 16384 the operand slabs of one
-# wave of tiles do not survive in L2 until the next wave; algorithmic bytes are 0.47 GB per launch).
-# cfg5 was not captured (same kernel as cfg4 at half the rows).
-NCU_TRAFFIC_BYTES = {"cfg1": None, "cfg4": 1.2108e9, "cfg2": 1.501e8, "cfg3": 1.508e8, "cfg5": None}
+# mean of its two launches (first GEMM 0.671 GB, second GEMM 1.779 GB: with K = 16384 the operand
+# slabs of one wave of tiles do not survive in L2 until the next wave; algorithmic bytes are
+# 0.47 GB per launch).  cfg5 was not captured (the same two kernels as cfg4, four times).
+NCU_TRAFFIC_BYTES = {"cfg1": None, "cfg4": 1.2248e9, "cfg2": 1.483e8, "cfg3": 1.504e8, "cfg5": None}
 
 
 def load_peaks():
@@ -760,6 +760,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="headline workload only (no `workloads` sub-records)")
     ap.add_argument("--no-graph", action="store_true", help="do not capture launch-bound steps in CUDA graphs")
+    ap.add_argument("--profile", action="store_true",
+                    help="for runs under a profiler: the K timed steps of the headline workload only (no sustained "
+                         "leg, no end-to-end leg, no other workloads, no CPU baseline, no CUDA graph)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -797,6 +800,14 @@ def main():
     scaling = args.scaling if name in SHARDED else "weak"
 
     wl = make_workload(name, world, scaling)
+    if args.profile:
+        head = measure(h, wl, name, W, steps, False, peaks, peak_src, world, sustained_s=0)
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "config": workload_config(name, world, scaling),
+                              "ms_per_step": head["ms_per_step"], "gpu_launches": head["gpu_launches"]}))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     head = measure(h, wl, name, W, steps, use_graph, peaks, peak_src, world)
     e2e = measure_e2e(h, wl, steps, world)
     wl = None
