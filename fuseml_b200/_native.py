@@ -27,13 +27,13 @@ BF16, F16, F32 = 0, 1, 2
 # opcodes ------------------------------------------------------------------------
 OP_NOP, OP_RELU, OP_GELU_ERF, OP_SIGMOID, OP_ADD_IMM, OP_MUL_IMM = 0, 1, 2, 3, 4, 5
 OP_ADD_T, OP_MUL_T, OP_SAVE, OP_SWAP, OP_ADD_SAVED, OP_MUL_SAVED = 6, 7, 8, 9, 10, 11
-OP_GELU_TANH, OP_STORE_AUX, OP_SUB_T, OP_RSUB_T, OP_GELU_ERF_MUL_SIGMOID = 12, 13, 14, 15, 16
+OP_GELU_TANH, OP_STORE_AUX, OP_SUB_T, OP_RSUB_T, OP_GELU_ERF_MUL_SIGMOID, OP_GELU_ERF_BWD_T = 12, 13, 14, 15, 16, 17
 OP_NAMES = {
     OP_NOP: "nop", OP_RELU: "relu", OP_GELU_ERF: "gelu_erf", OP_SIGMOID: "sigmoid",
     OP_ADD_IMM: "add_imm", OP_MUL_IMM: "mul_imm", OP_ADD_T: "add_t", OP_MUL_T: "mul_t",
     OP_SAVE: "save", OP_SWAP: "swap", OP_ADD_SAVED: "add_saved", OP_MUL_SAVED: "mul_saved",
     OP_GELU_TANH: "gelu_tanh", OP_STORE_AUX: "store_aux", OP_SUB_T: "sub_t", OP_RSUB_T: "rsub_t",
-    OP_GELU_ERF_MUL_SIGMOID: "gelu_erf_mul_sigmoid",
+    OP_GELU_ERF_MUL_SIGMOID: "gelu_erf_mul_sigmoid", OP_GELU_ERF_BWD_T: "gelu_erf_bwd_t",
 }
 
 # reductions ---------------------------------------------------------------------
@@ -69,6 +69,7 @@ class GemmDesc(C.Structure):
         ("ops", EpiOp * MAX_EPI_OPS),
         ("operands", Operand * MAX_OPERANDS),
         ("reduce", Reduce),
+        ("a_stride_k", C.c_int64),
     ]
 
 

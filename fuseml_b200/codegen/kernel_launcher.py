@@ -322,8 +322,7 @@ class KernelLauncher:
         if p.views is not None:
             input_tensors = self._apply_views(input_tensors, p.views)
         left, right = input_tensors[self._left_idx], input_tensors[self._right_idx]
-        if left.stride(1) != 1 and p.K != 1:
-            left = left.contiguous()
+        left = K.addressable_left(left, right)      # same decision as when the descriptor was prepared
         device = left.device
         desc.a = left.data_ptr()
         desc.b = right.data_ptr()

@@ -211,6 +211,59 @@ __device__ __forceinline__ void fold_operand_chunk(float (&v)[CH], int32_t code,
   }
 }
 
+// Derivative of GELU (erf form) at two points: gelu'(x) = Phi(x) + x phi(x)
+//   = 0.5 (1 + erf(x / sqrt 2)) + x exp(-x^2 / 2) / sqrt(2 pi),
+// with the same erfc approximation as gelu_erf2; the exponential is shared by both terms.
+__device__ __forceinline__ void gelu_erf_grad2(float& x0, float& x1) {
+  const f32x2 x = pack2(x0, x1);
+  const f32x2 ax = pack2(fabsf(x0), fabsf(x1));
+  const f32x2 den = fma2(ax, splat2(0.3275911f * 0.70710678118654752440f), splat2(1.0f));
+  float d0, d1;
+  unpack2(den, d0, d1);
+  const f32x2 t = pack2(rcp_approx(d0), rcp_approx(d1));
+  f32x2 poly = fma2(t, splat2(1.061405429f), splat2(-1.453152027f));
+  poly = fma2(poly, t, splat2(1.421413741f));
+  poly = fma2(poly, t, splat2(-0.284496736f));
+  poly = fma2(poly, t, splat2(0.254829592f));
+  poly = mul2(poly, t);
+  float a0, a1;
+  unpack2(mul2(mul2(x, x), splat2(-0.5f * 1.4426950408889634f)), a0, a1);
+  const f32x2 e = pack2(ex2_approx(a0), ex2_approx(a1));                 // exp(-x^2 / 2)
+  float r0, r1;
+  unpack2(fma2(poly, mul2(e, splat2(-1.0f)), splat2(1.0f)), r0, r1);   // |erf(x / sqrt 2)|
+  const f32x2 erf = pack2(copysignf(r0, x0), copysignf(r1, x1));
+  const f32x2 cdf = fma2(erf, splat2(0.5f), splat2(0.5f));
+  unpack2(fma2(mul2(x, e), splat2(0.3989422804014327f), cdf), x0, x1);
+}
+
+// t[i] = operand[m, n0 + i] as fp32 for the CH columns of a chunk (0 for columns >= N).
+template <int CH>
+__device__ __forceinline__ void load_operand_chunk(float (&t)[CH], const EpiOperand& o, int64_t m, int32_t n0, int32_t N) {
+  const int64_t base = m * o.stride_m + static_cast<int64_t>(n0) * o.stride_n;
+  if (o.stride_n == 1 && n0 + CH <= N && o.dtype != FUSEML_F32) {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(o.ptr) + base;
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+#pragma unroll
+      for (int i = 0; i < CH / 8; ++i) {
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(p) + i);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f;
+          if (o.dtype == FUSEML_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+          else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+          t[8 * i + 2 * j] = f.x;
+          t[8 * i + 2 * j + 1] = f.y;
+        }
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CH; ++i)
+    t[i] = (n0 + i < N) ? load_scalar(o.ptr, base + static_cast<int64_t>(i) * o.stride_n, o.dtype) : 0.0f;
+}
+
 // v[i] (+|*)= src[i], src = CH fp32 values staged in shared memory (same address for every
 // lane: the reads broadcast)
 template <bool kMul, int CH>
@@ -433,6 +486,17 @@ __device__ __forceinline__ void run_program(const GemmParams& p, int64_t m, int3
           if constexpr (CH == 16) fold_tile_smem(v, code == FUSEML_OP_MUL_T, mat_piece, p.operands[p.ops[op].slot].dtype);
         } else if (row_ok) {
           fold_operand_chunk<CH>(v, code, p.operands[p.ops[op].slot], m, n0, p.N);
+        }
+      } break;
+      case FUSEML_OP_GELU_ERF_BWD_T: {
+        if (row_ok) {
+          float t[CH];
+          load_operand_chunk<CH>(t, p.operands[p.ops[op].slot], m, n0, p.N);
+#pragma unroll
+          for (int i = 0; i < CH; i += 2) {
+            gelu_erf_grad2(t[i], t[i + 1]);
+            unpack2(mul2(pack2(v[i], v[i + 1]), pack2(t[i], t[i + 1])), v[i], v[i + 1]);
+          }
         }
       } break;
       case FUSEML_OP_STORE_AUX: {

@@ -78,11 +78,11 @@ struct InstanceState {
   int max_clusters[kMaxDevices] = {0};
 };
 
-template <int BN, int STAGES, bool B_MN, int PROG, int CG, int EW>
+template <int BN, int STAGES, int LAYOUT, int PROG, int CG, int EW>
 static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tr, const CUtensorMap& td,
                            const GemmParams& p, int grid, cudaStream_t stream) {
   using L = v2::Smem<BN, STAGES, CG>;
-  auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, B_MN, PROG, CG, EW>;
+  auto kernel = v2::gemm_epilogue_kernel_v2<BN, STAGES, LAYOUT, PROG, CG, EW>;
   static InstanceState state;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return FUSEML_E_DEVICE; }
@@ -155,11 +155,13 @@ static int classify_program(const GemmParams& p) {
 
 template <int BN, int STAGES, int CG, int EW = 8>
 static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tr, const CUtensorMap& td,
-                     const GemmParams& p, bool b_mn, int grid, cudaStream_t stream) {
+                     const GemmParams& p, int layout, int grid, cudaStream_t stream) {
+  // layout: 0 = A and B K-major, 1 = B MN-major, 2 = A and B MN-major (see the kernel)
 #define FUSEML_DISPATCH(PROG)                                                                             \
   case PROG:                                                                                              \
-    return b_mn ? launch_instance<BN, STAGES, true, PROG, CG, EW>(ta, tb, tr, td, p, grid, stream)        \
-                : launch_instance<BN, STAGES, false, PROG, CG, EW>(ta, tb, tr, td, p, grid, stream)
+    return layout == 2 ? launch_instance<BN, STAGES, 2, PROG, CG, EW>(ta, tb, tr, td, p, grid, stream)    \
+         : layout == 1 ? launch_instance<BN, STAGES, 1, PROG, CG, EW>(ta, tb, tr, td, p, grid, stream)    \
+                       : launch_instance<BN, STAGES, 0, PROG, CG, EW>(ta, tb, tr, td, p, grid, stream)
   switch (classify_program(p)) {
     FUSEML_DISPATCH(epi::kProgGenericSaved);
     FUSEML_DISPATCH(epi::kProgBiasGelu);
@@ -326,7 +328,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   const int bl = b_layout(desc);
   const void* a_ptr = desc->a;
   const void* b_ptr = desc->b;
-  int64_t K = desc->K, lda = desc->lda, ldb = (bl == 0) ? desc->b_stride_n : desc->b_stride_k;
+  bool a_mn = a_layout(desc) == 1;
+  int64_t K = desc->K, lda = a_mn ? desc->a_stride_k : desc->lda, ldb = (bl == 0) ? desc->b_stride_n : desc->b_stride_k;
   bool b_mn = (bl == 1);
   if (f32) {
     // expand both operands to [rows, 3K] K-major copies in the workspace
@@ -335,7 +338,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     float* b2 = reinterpret_cast<float*>(ws + w.split_b_off);
     const int threads = 256;
     const int64_t ta = desc->M * desc->K, tb = desc->N * desc->K;
-    SplitJob ja = {reinterpret_cast<const float*>(desc->a), desc->M, desc->K, desc->lda, 1, 0, a2, ld,
+    SplitJob ja = {reinterpret_cast<const float*>(desc->a), desc->M, desc->K, desc->lda, a_mn ? desc->a_stride_k : 1, 0, a2, ld,
                    static_cast<int32_t>(std::min<int64_t>((ta + threads - 1) / threads, 148 * 8))};
     SplitJob jb = {reinterpret_cast<const float*>(desc->b), desc->N, desc->K, desc->b_stride_n, desc->b_stride_k, 1, b2, ld,
                    static_cast<int32_t>(std::min<int64_t>((tb + threads - 1) / threads, 148 * 8))};
@@ -343,13 +346,15 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     // one launch for both operands
     split_tf32_kernel<<<ja.blocks + jb.blocks, threads, 0, stream>>>(ja, jb);
     if (cudaGetLastError() != cudaSuccess) return FUSEML_E_LAUNCH;
-    a_ptr = a2; b_ptr = b2; K = 3 * desc->K; lda = ld; ldb = ld; b_mn = false;
+    a_ptr = a2; b_ptr = b2; K = 3 * desc->K; lda = ld; ldb = ld; b_mn = false; a_mn = false;
   }
+  const int layout = a_mn ? 2 : (b_mn ? 1 : 0);
 
   const int BN = plan.tile_n;          // run-time tile width; kernels are built for 128 and 256
   const int BK = f32 ? 32 : 64;
   CUtensorMap ta, tb;
-  rc = encode_2d(&ta, desc->ab_dtype, a_ptr, desc->M, K, lda, BK, kTileM);
+  if (!a_mn) rc = encode_2d(&ta, desc->ab_dtype, a_ptr, desc->M, K, lda, BK, kTileM);
+  else rc = encode_2d(&ta, desc->ab_dtype, a_ptr, K, desc->M, lda, 64, BK);     // stored [K, M]: boxes of 64 k x 64 m
   if (rc != FUSEML_OK) return rc;
   // K-major B: one box per CTA covers that CTA's share of the tile's columns (all of them for a
   // single CTA, half for a CTA pair)
@@ -443,8 +448,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     std::memset(&none, 0, sizeof(none));
     const int items = p.num_tiles * slices;
     if (slices > 1) {
-      if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, none, none, pg, b_mn, items, stream);
-      else rc = launch_bn<128, 6, 1>(ta, tb, none, none, pg, b_mn, items, stream);
+      if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, none, none, pg, layout, items, stream);
+      else rc = launch_bn<128, 6, 1>(ta, tb, none, none, pg, layout, items, stream);
       if (rc != FUSEML_OK) return rc;
       GemmParams pf = p;
       pf.split_k = slices;
@@ -492,12 +497,12 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
         encode_2d(&td, p.out_dtype, p.d, desc->M, desc->N, p.ldd, 64, kTileM) == FUSEML_OK) {
       p.io_flags |= 2;
     }
-    if (CGr == 2) rc = launch_bn<256, 6, 2, 16>(ta, tb, tr, td, p, b_mn, grid, stream);
-    else if (BN > 128) rc = launch_bn<256, 4, 1, 16>(ta, tb, tr, td, p, b_mn, grid, stream);
-    else rc = launch_bn<128, 6, 1, 16>(ta, tb, tr, td, p, b_mn, grid, stream);
-  } else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, tr, td, p, b_mn, grid, stream);
-  else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, tr, td, p, b_mn, grid, stream);
-  else rc = launch_bn<128, 6, 1>(ta, tb, tr, td, p, b_mn, grid, stream);
+    if (CGr == 2) rc = launch_bn<256, 6, 2, 16>(ta, tb, tr, td, p, layout, grid, stream);
+    else if (BN > 128) rc = launch_bn<256, 4, 1, 16>(ta, tb, tr, td, p, layout, grid, stream);
+    else rc = launch_bn<128, 6, 1, 16>(ta, tb, tr, td, p, layout, grid, stream);
+  } else if (CGr == 2) rc = launch_bn<256, 6, 2>(ta, tb, tr, td, p, layout, grid, stream);
+  else if (BN > 128) rc = launch_bn<256, 4, 1>(ta, tb, tr, td, p, layout, grid, stream);
+  else rc = launch_bn<128, 6, 1>(ta, tb, tr, td, p, layout, grid, stream);
   if (rc != FUSEML_OK) return rc;
 
   if (desc->reduce.kinds != 0) {

@@ -108,7 +108,8 @@ __device__ __forceinline__ void prefetch_operands(const GemmParams& p, int64_t m
                                                   bool row_ok, int lane) {
   for (int op = 0; op < p.n_ops; ++op) {
     const int32_t code = p.ops[op].opcode;
-    if (code != FUSEML_OP_ADD_T && code != FUSEML_OP_MUL_T && code != FUSEML_OP_SUB_T && code != FUSEML_OP_RSUB_T)
+    if (code != FUSEML_OP_ADD_T && code != FUSEML_OP_MUL_T && code != FUSEML_OP_SUB_T && code != FUSEML_OP_RSUB_T &&
+        code != FUSEML_OP_GELU_ERF_BWD_T)
       continue;
     const EpiOperand& o = p.operands[p.ops[op].slot];
     if (o.stride_n != 1) continue;
@@ -126,16 +127,19 @@ __device__ __forceinline__ void prefetch_operands(const GemmParams& p, int64_t m
   }
 }
 
-// B_MN: B is row-major [K,N] in global memory (MN-major tiles) instead of K-major.  PROG: how
-// the epilogue program runs (epi::kProg*).  CG: CTAs per tile (1 or 2).  EW: epilogue warps.
+// LAYOUT: 0 = A and B K-major (activations x nn.Linear weight view), 1 = B row-major [K,N]
+// (MN-major tiles), 2 = A stored [K,M] as well (both MN-major: weight gradients, dY^T @ X).  PROG:
+// how the epilogue program runs (epi::kProg*).  CG: CTAs per tile (1 or 2).  EW: epilogue warps.
 // The operand format (f16 / bf16 / tf32) is a run-time value (GemmParams::fmt): it only selects
 // the instruction descriptor, the MMA kind and the K extent of a stage.
-template <int BN, int STAGES, bool B_MN, int PROG, int CG, int EW>
+template <int BN, int STAGES, int LAYOUT, int PROG, int CG, int EW>
 __global__ void __launch_bounds__(threads_for(EW), 1)
 gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_r, const __grid_constant__ CUtensorMap tmap_d,
                         const __grid_constant__ GemmParams p) {
   using L = Smem<BN, STAGES, CG>;
+  constexpr bool B_MN = LAYOUT >= 1;
+  constexpr bool A_MN = LAYOUT == 2;
   const bool tf32 = p.fmt == 2;
   const int32_t BK = tf32 ? 32 : 64;             // elements per 128-byte stage row
   constexpr int kKSteps = 4;                      // MMAs per stage: 32 bytes of K each (16 x 16-bit or 8 x tf32)
@@ -255,6 +259,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       bool ok = true;
       const uint64_t pol_stream = ptx::policy_evict_first();
       const uint64_t pol_keep = ptx::policy_evict_last();
+      const uint64_t pol_normal = ptx::policy_evict_normal();
       long long st_empty = 0;
       for (int32_t t = first_tile; t < p.num_tiles && ok; t += tile_step) {
         int32_t tm, tn;
@@ -281,10 +286,19 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           // 2 = evict-last (keep resident).  The loads are spelled out per case: routing them
           // through a helper with run-time policy and box-count tests made the issue of the four
           // MN-major boxes slow enough to starve the tensor core.
-          const uint64_t pol_a = p.a_stream == 1 ? pol_stream : pol_keep;
+          const uint64_t pol_a = p.a_stream == 1 ? pol_stream : (p.a_stream == 2 ? pol_keep : pol_normal);
           const uint64_t pol_b = p.b_stream == 1 ? pol_stream : pol_keep;
+          if (A_MN) {
+            // A stored [K, M]: two boxes of 64 k x 64 m (the same shape as an MN-major B box)
+#pragma unroll
+            for (int j = 0; j < kTileM / 64; ++j) {
+              if (CG == 1) ptx::tma_load_2d_hint(a_dst + j * kMnBoxBytes, &tmap_a, bar, m0 + j * 64, kb * BK, pol_a);
+              else ptx::tma_load_2d_pair_hint(a_dst + j * kMnBoxBytes, &tmap_a, bar, m0 + j * 64, kb * BK, pol_a);
+            }
+          }
           if (CG == 1) {
-            if (p.a_stream == 0) ptx::tma_load_2d(a_dst, &tmap_a, bar, kb * BK, m0);
+            if (A_MN) {}
+            else if (p.a_stream == 0) ptx::tma_load_2d(a_dst, &tmap_a, bar, kb * BK, m0);
             else ptx::tma_load_2d_hint(a_dst, &tmap_a, bar, kb * BK, m0, pol_a);
             if (!B_MN) {
               if (p.b_stream == 0) ptx::tma_load_2d(b_dst, &tmap_b, bar, kb * BK, n0);
@@ -298,7 +312,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 ptx::tma_load_2d_hint(b_dst + j * kMnBoxBytes, &tmap_b, bar, n0 + j * 64, kb * BK, pol_b);
             }
           } else {
-            if (p.a_stream == 0) ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, kb * BK, m0);
+            if (A_MN) {}
+            else if (p.a_stream == 0) ptx::tma_load_2d_pair(a_dst, &tmap_a, bar, kb * BK, m0);
             else ptx::tma_load_2d_pair_hint(a_dst, &tmap_a, bar, kb * BK, m0, pol_a);
             if (!B_MN) {
               if (p.b_stream == 0) ptx::tma_load_2d_pair(b_dst, &tmap_b, bar, kb * BK, n0);
@@ -390,7 +405,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     // costs the single issuing thread about 3 % of a tensor-bound GEMM.
     auto mma_role = [&](auto tf32_tag) {
       constexpr bool kTf32 = decltype(tf32_tag)::value;
-      const uint32_t idesc = ptx::make_idesc(static_cast<uint32_t>(p.fmt), 0u, B_MN ? 1u : 0u, kTileM * CG, static_cast<uint32_t>(bn));
+      const uint32_t idesc = ptx::make_idesc(static_cast<uint32_t>(p.fmt), A_MN ? 1u : 0u, B_MN ? 1u : 0u, kTileM * CG, static_cast<uint32_t>(bn));
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -398,7 +413,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       bool ok = true;
       long long st_full = 0, st_tmem = 0;
       bool ready = false;   // the next ring stage is already known to be full
-      const uint64_t a_desc0 = ptx::make_smem_desc_sw128(smem_base, 16u, 1024u);
+      const uint64_t a_desc0 = A_MN ? ptx::make_smem_desc_sw128(smem_base, kMnBoxBytes, 1024u)
+                                    : ptx::make_smem_desc_sw128(smem_base, 16u, 1024u);
       const uint64_t b_desc0 = B_MN ? ptx::make_smem_desc_sw128(smem_base + L::kABytes, kMnBoxBytes, 1024u)
                                     : ptx::make_smem_desc_sw128(smem_base + L::kABytes, 16u, 1024u);
 #ifdef FUSEML_STALL_COUNTERS
@@ -434,7 +450,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           // that changes from stage to stage
           const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(stage) * (L::kStageBytes >> 4);
           const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(stage) * (L::kStageBytes >> 4);
-          constexpr uint32_t kAStep = 32u >> 4;
+          constexpr uint32_t kAStep = A_MN ? ((16 * kSwizzleBytes) >> 4) : (32u >> 4);
           constexpr uint32_t kBStep = B_MN ? ((16 * kSwizzleBytes) >> 4) : (32u >> 4);
 #pragma unroll
           for (int k = 0; k < kKSteps; ++k) {

@@ -45,7 +45,16 @@ void default_props(fuseml_device_props_t* p) {
 
 static bool op_uses_operand(int32_t opcode) {
   return opcode == FUSEML_OP_ADD_T || opcode == FUSEML_OP_MUL_T || opcode == FUSEML_OP_SUB_T ||
-         opcode == FUSEML_OP_RSUB_T || opcode == FUSEML_OP_STORE_AUX;
+         opcode == FUSEML_OP_RSUB_T || opcode == FUSEML_OP_STORE_AUX || opcode == FUSEML_OP_GELU_ERF_BWD_T;
+}
+
+int a_layout(const fuseml_gemm_desc_t* d) {
+  if (d->a_stride_k == 0 || d->a_stride_k == 1) return 0;
+  if (d->lda != 1 && d->M > 1) return -1;
+  if (d->ab_dtype == FUSEML_F32) return 1;                      // expanded by plain loads: any stride
+  const int eb = dtype_bytes(d->ab_dtype);
+  if (d->a_stride_k < d->M || (d->a_stride_k * eb) % 16 != 0) return -1;
+  return b_layout(d) == 1 ? 1 : -1;                             // kernels exist for MN-major A with MN-major B only
 }
 
 int b_layout(const fuseml_gemm_desc_t* d) {
@@ -76,11 +85,13 @@ int validate_desc(const fuseml_gemm_desc_t* d) {
     // stride works there.)
     if ((reinterpret_cast<uintptr_t>(d->a) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d->b) & 15u) != 0)
       return FUSEML_E_LAYOUT;
-    if (d->M > 1 && (d->lda < d->K || (d->lda * eb) % 16 != 0)) return FUSEML_E_LAYOUT;
-  } else if (d->M > 1 && d->lda < d->K) {
+    if (d->a_stride_k <= 1 && d->M > 1 && (d->lda < d->K || (d->lda * eb) % 16 != 0)) return FUSEML_E_LAYOUT;
+  } else if (d->a_stride_k <= 1 && d->M > 1 && d->lda < d->K) {
     return FUSEML_E_LAYOUT;
   }
+  if (d->a_stride_k < 0) return FUSEML_E_LAYOUT;
   if (b_layout(d) < 0) return FUSEML_E_LAYOUT;
+  if (a_layout(d) < 0) return FUSEML_E_LAYOUT;
   if (d->n_ops < 0 || d->n_ops > FUSEML_MAX_EPI_OPS) return FUSEML_E_EPILOGUE;
   if (d->n_operands < 0 || d->n_operands > FUSEML_MAX_OPERANDS) return FUSEML_E_EPILOGUE;
   for (int i = 0; i < d->n_ops; ++i) {

@@ -17,6 +17,8 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props, f
 // How B sits in memory: 0 = K contiguous (nn.Linear weight view), 1 = N
 // contiguous (row-major [K,N]), -1 = neither can be described by a TMA map.
 int b_layout(const fuseml_gemm_desc_t* d);
+// How A sits in memory: 0 = K contiguous, 1 = M contiguous (stored [K,M]), -1 = not addressable.
+int a_layout(const fuseml_gemm_desc_t* d);
 
 // Leading dimension (elements) of the [rows, 3K] hi|lo|hi split copies that
 // fp32 operands are expanded into before the TF32 MMA.

@@ -77,6 +77,10 @@ class EpilogueProgram:
     def rsub_tensor(self, t: torch.Tensor) -> "EpilogueProgram":
         return self._push(N.OP_RSUB_T, slot=self._slot(t))
 
+    def gelu_backward(self, pre: torch.Tensor) -> "EpilogueProgram":
+        """``acc *= gelu'(pre)``: ``aten.gelu_backward(grad=acc, self=pre)``, erf form."""
+        return self._push(N.OP_GELU_ERF_BWD_T, slot=self._slot(pre))
+
     def bias(self, b: torch.Tensor) -> "EpilogueProgram":
         """``acc += bias`` — the addmm bias (fuseml/codegen/kernel_generator.py:885-901)."""
         return self.add_tensor(b)
@@ -148,6 +152,22 @@ def _broadcast_strides(t: torch.Tensor, M: int, Ncols: int) -> tuple[int, int]:
     raise N.NativeLibraryError("epilogue operands must have at most 2 dimensions")
 
 
+def addressable_left(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a`` itself when the kernel can read it in place, else a row-major copy.  K contiguous is
+    the usual case.  A transposed view (stored ``[K, M]``: the ``dY^T`` of a weight gradient) is
+    read in place when B is row-major ``[K, N]`` too and the pitch is a multiple of 16 bytes;
+    fp32 operands are expanded by plain loads and take any strides."""
+    M, K = a.shape
+    if K == 1 or a.stride(1) == 1:
+        return a
+    if a.dtype == torch.float32:
+        return a if min(a.stride()) >= 0 else a.contiguous()
+    if (a.stride(0) == 1 or M == 1) and a.stride(1) >= M and (a.stride(1) * a.element_size()) % 16 == 0 \
+            and a.data_ptr() % 16 == 0 and b.stride(1) == 1:
+        return a
+    return a.contiguous()
+
+
 def fill_desc(desc: N.GemmDesc, a: torch.Tensor, b: torch.Tensor, program: EpilogueProgram | None,
               out: torch.Tensor | None, out_dtype: torch.dtype) -> tuple[int, int, int]:
     """Write the GEMM part of a descriptor; returns (M, N, K)."""
@@ -161,11 +181,11 @@ def fill_desc(desc: N.GemmDesc, a: torch.Tensor, b: torch.Tensor, program: Epilo
         raise N.NativeLibraryError(f"contracting dimension mismatch: A{tuple(a.shape)} B{tuple(b.shape)}")
     if a.dtype != b.dtype:
         raise N.NativeLibraryError(f"A and B dtypes differ: {a.dtype} vs {b.dtype}")
-    if a.stride(1) != 1 and K != 1:
-        a = a.contiguous()  # K must be contiguous in A; rare (transposed activations)
+    a = addressable_left(a, b)
     desc.M, desc.N, desc.K = M, Ncols, K
     desc.a = a.data_ptr()
     desc.lda = a.stride(0)
+    desc.a_stride_k = a.stride(1) if K != 1 else 1
     desc.b = b.data_ptr()
     desc.b_stride_k = b.stride(0)
     desc.b_stride_n = b.stride(1)

@@ -84,7 +84,10 @@ enum {
                              /*   diamond SAVE, GELU_ERF, SWAP, SIGMOID, MUL_SAVED (either     */
                              /*   branch order) is rewritten to it at launch when `saved` is   */
                              /*   not read again; half the special-function work              */
-  FUSEML_OP__COUNT = 17
+  FUSEML_OP_GELU_ERF_BWD_T = 17, /* acc *= gelu'(operand[slot][m,n]), gelu' = Phi(x) + x phi(x):  */
+                             /*   aten.gelu_backward(grad = acc, self = operand), the epilogue   */
+                             /*   of the data-gradient GEMM of a Linear -> GELU pair            */
+  FUSEML_OP__COUNT = 18
 };
 
 #define FUSEML_MAX_EPI_OPS 16
@@ -134,7 +137,8 @@ typedef struct {
 /* ---- the GEMM problem --------------------------------------------------- */
 typedef struct {
   int64_t M, N, K;
-  /* A[M,K]: element (m,k) at a[m*lda + k]; K contiguous.                     */
+  /* A[M,K]: element (m,k) at a[m*lda + k*a_stride_k] (a_stride_k is the last field of this
+   * struct; left at 0 it means 1: K contiguous).                                          */
   const void* a;
   int64_t lda;
   /* B[K,N]: element (k,n) at b[k*b_stride_k + n*b_stride_n]; exactly one of
@@ -155,6 +159,11 @@ typedef struct {
   fuseml_epi_op_t ops[FUSEML_MAX_EPI_OPS];
   fuseml_operand_t operands[FUSEML_MAX_OPERANDS];
   fuseml_reduce_t reduce;
+  /* Stride of A along K, in elements: element (m,k) at a[m*lda + k*a_stride_k].  0 or 1: K is
+   * contiguous (the usual activation matrix).  Otherwise lda must be 1: A is stored [K,M]
+   * (a transposed view, as in a weight gradient dY^T @ X); 16-bit operands then need B row-major
+   * [K,N] as well (b_stride_n == 1) and a_stride_k * element size a multiple of 16 bytes. */
+  int64_t a_stride_k;
 } fuseml_gemm_desc_t;
 
 /* ---- plan: what the roofline router decides ----------------------------- */

@@ -90,6 +90,13 @@ def sigmoid(x):
     return (1.0 / (1.0 + np.exp(-x64))).astype(np.float32)
 
 
+def gelu_erf_grad(x):
+    """d/dx of the erf-form GELU: ``Phi(x) + x * phi(x)`` (what ``aten.gelu_backward`` multiplies the
+    incoming gradient by; the reference leaves backward graphs to PyTorch, fuseml/compiler.py:214-218)."""
+    x64 = x.astype(np.float64)
+    return (0.5 * (1.0 + _erf(x64 * 0.7071067811865476)) + x64 * np.exp(-0.5 * x64 * x64) / np.sqrt(2.0 * np.pi)).astype(np.float32)
+
+
 def _bcast(t: np.ndarray, M: int, N: int) -> np.ndarray:
     """Broadcast rule for external operands: a 1-D tensor of length N runs along
     columns, of length M along rows (fuseml/codegen/kernel_generator.py:270-277);
@@ -111,7 +118,7 @@ def run_epilogue(acc: np.ndarray, ops: Sequence[tuple], aux_dtype: str = "bf16")
 
     ``("relu",)``, ``("gelu",)``, ``("gelu_tanh",)``, ``("sigmoid",)``, ``("gelu_times_sigmoid",)``,
     ``("add_scalar", c)``, ``("mul_scalar", c)``,
-    ``("add", t)``, ``("mul", t)``, ``("sub", t)``, ``("rsub", t)`` with an external array,
+    ``("add", t)``, ``("mul", t)``, ``("sub", t)``, ``("rsub", t)``, ``("gelu_bwd", t)`` with an external array,
     ``("save",)``, ``("swap",)``, ``("add_saved",)``, ``("mul_saved",)``,
     ``("store_aux",)`` (returns the value at that point, cast to ``aux_dtype``).
 
@@ -143,6 +150,8 @@ def run_epilogue(acc: np.ndarray, ops: Sequence[tuple], aux_dtype: str = "bf16")
             v = (v * _bcast(op[1], M, N)).astype(np.float32)
         elif k == "sub":
             v = (v - _bcast(op[1], M, N)).astype(np.float32)
+        elif k == "gelu_bwd":
+            v = (v.astype(np.float64) * gelu_erf_grad(_bcast(op[1], M, N)).astype(np.float64)).astype(np.float32)
         elif k == "rsub":
             v = (_bcast(op[1], M, N) - v).astype(np.float32)
         elif k == "save":

@@ -183,7 +183,7 @@ def test_struct_layout_matches_header():
     assert C.sizeof(N.EpiOp) == 16
     assert C.sizeof(N.Operand) == 32
     assert C.sizeof(N.Reduce) == 48
-    assert C.sizeof(N.GemmDesc) == 656
+    assert C.sizeof(N.GemmDesc) == 664
     assert C.sizeof(N.Plan) == 96
     assert C.sizeof(N.DeviceProps) == 40
 

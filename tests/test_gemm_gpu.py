@@ -42,7 +42,9 @@ def _program(K, ops, env):
     prog = K.EpilogueProgram()
     for op in ops:
         k = op[0]
-        if k in ("bias", "add"):
+        if k == "gelu_bwd":
+            prog.gelu_backward(env[op[1]])
+        elif k in ("bias", "add"):
             prog.add_tensor(env[op[1]])
         elif k == "mul":
             prog.mul_tensor(env[op[1]])
@@ -195,6 +197,25 @@ def test_tile_widths_and_cta_pairs(K, b_view):
         np.testing.assert_allclose(out.float().cpu().numpy(), ref, err_msg=f"tile_n={tile_n} cluster={cluster}", **BF16_TOL)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("M,Kd,Nn", [(256, 512, 384), (200, 136, 304), (1000, 4096, 520), (72, 8192, 256)])
+def test_transposed_left_operand_is_read_in_place(K, M, Kd, Nn, dtype):
+    """A stored [K, M] (the dY^T of a weight gradient, dW = dY^T @ X, where K is the token
+    dimension) with B row-major [K, N]: both operands MN-major, no copy of either."""
+    td = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    g = torch.Generator().manual_seed(M + Kd + Nn)
+    a_t = torch.randn(Kd, M, generator=g).to(td)                 # dY: [tokens, out_features]
+    b = (torch.randn(Kd, Nn, generator=g) / Kd ** 0.5).to(td)     # X:  [tokens, in_features]
+    ref = chain.fused_chain(a_t.float().numpy().T, b.float().numpy(), (), out_dtype=dtype)["d"]
+    a_dev = a_t.cuda().t()
+    assert K.addressable_left(a_dev, b.cuda()) is a_dev, "the view is passed as it is"
+    out = K.fused_gemm(a_dev, b.cuda())
+    torch.cuda.synchronize()
+    _status_ok(K)
+    tol = {"bf16": BF16_TOL, "f16": dict(rtol=2e-3, atol=2e-3), "f32": dict(rtol=1e-4, atol=1e-4)}[dtype]
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, **tol)
+
+
 def test_strided_views_without_copies(K):
     """Row-strided A, row-strided output and a column-sliced weight are addressed in place."""
     g = torch.Generator().manual_seed(4)
@@ -259,6 +280,8 @@ EPILOGUES = {
     "dag_saved_read_again": lambda: [("save",), ("gelu",), ("swap",), ("sigmoid",), ("mul_saved",), ("add_saved",)],
     "gelu_times_sigmoid_op": lambda: [("bias", "row"), ("gelu_times_sigmoid",), ("add", "full")],
     "dag_add_saved": lambda: [("save",), ("relu",), ("add_saved",)],
+    "gelu_backward": lambda: [("gelu_bwd", "full")],
+    "gelu_backward_fp32_operand_then_residual": lambda: [("gelu_bwd", "full32"), ("add", "full")],
     "long_chain": lambda: [("bias", "row"), ("relu",), ("mul_scalar", 2.0), ("add", "full"), ("sigmoid",),
                            ("mul", "col"), ("add_scalar", -0.25), ("gelu",)],
 }
