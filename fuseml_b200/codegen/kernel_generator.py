@@ -228,6 +228,14 @@ class Sm100KernelGenerator:
             elif tgt is _aten.gelu.default:
                 approx = node.kwargs.get("approximate", "none")
                 steps.append(EpiStep(N.OP_GELU_TANH if approx == "tanh" else N.OP_GELU_ERF))
+            elif tgt is _aten.gelu_backward.default:
+                # gelu_backward(grad, self, approximate): grad is the chain value, self a saved activation
+                approx = node.kwargs.get("approximate", args[2] if len(args) > 2 else "none")
+                if approx != "none":
+                    raise UnsupportedChainError(f"{node.name}: gelu_backward(approximate={approx!r}) has no epilogue op")
+                if len(inside) != 1 or resolve(args[0]) is not acc_of:
+                    raise UnsupportedChainError(f"{node.name}: the chain value must be the gradient argument")
+                steps.append(EpiStep(N.OP_GELU_ERF_BWD_T, input_index(args[1])))
             elif tgt in _ADD or tgt in _MUL:
                 is_add = tgt in _ADD
                 alpha = float(node.kwargs.get("alpha", 1)) if is_add else 1.0

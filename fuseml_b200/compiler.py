@@ -90,15 +90,20 @@ class FuseMLCompiler:
 
     def __init__(self, registry: SupportedOpsRegistry | None = None, *, dag_epilogue: bool = True,
                  multi_reduction: bool = True, global_reductions: bool = True, bare_trigger: bool = True,
-                 plan_cache: Any = None, autotune: bool | None = None) -> None:
+                 backward: bool = True, plan_cache: Any = None, autotune: bool | None = None) -> None:
         self.registry: SupportedOpsRegistry = registry or build_default_registry()
         self.fusion_candidates: list = []
         self.fusion_applied: bool = False
         self.fusion_strategy: str = "none"
         self.launchers: list[KernelLauncher] = []
+        # launchers put into backward graphs (a subset of `launchers`); `backward=False` leaves
+        # backward graphs to PyTorch, as the reference does (it passes only a forward compiler,
+        # fuseml/compiler.py:214-218)
+        self.backward_launchers: list[KernelLauncher] = []
+        self.fuse_backward = bool(backward)
         self.declined: list[tuple[str, str]] = []
         self._options = dict(dag_epilogue=dag_epilogue, multi_reduction=multi_reduction,
-                             global_reductions=global_reductions, bare_trigger=bare_trigger)
+                             global_reductions=global_reductions, bare_trigger=bare_trigger, backward_ops=True)
         self._generator = Sm100KernelGenerator()
         self._cache = KernelCache()
         # Measured launch plans on disk (codegen/plan_cache.py).  `plan_cache` is a PlanCache, a
@@ -124,7 +129,19 @@ class FuseMLCompiler:
             return make_boxed_func(self._compile_aten_graph(aten_gm, aten_inputs))
 
         def bw_compiler(aten_gm: torch.fx.GraphModule, aten_inputs: list) -> Callable:
-            return make_boxed_func(aten_gm.forward)   # backward graphs are not fused
+            # Backward graphs go through the same discovery: dgrad GEMMs with their pointwise tails
+            # (mm -> gelu_backward, mm -> add of the residual's gradient) and the wgrad GEMMs
+            # dY^T @ X, whose transposed left operand the kernel reads in place.  A backward graph
+            # with nothing to fuse, or any failure to lower it, leaves it to PyTorch.
+            if self.fuse_backward:
+                n_before = len(self.launchers)
+                try:
+                    fn = self._compile_aten_graph(aten_gm, aten_inputs)
+                    self.backward_launchers.extend(self.launchers[n_before:])
+                    return make_boxed_func(fn)
+                except _NoFusionPossible as exc:
+                    logger.info("backward graph left to PyTorch: %s", exc)
+            return make_boxed_func(aten_gm.forward)
 
         try:
             return aot_module_simplified(gm, example_inputs, fw_compiler=fw_compiler, bw_compiler=bw_compiler,

@@ -20,7 +20,10 @@ by default so that structural behaviour stays drop-in):
 * ``global_reductions`` whole-tensor ``sum`` / ``amax`` / ``mean`` are accepted as reduction tails;
 * ``bare_trigger``      an ``addmm`` / ``mm`` that absorbs nothing is still a group (the reference drops
                         it, fuseml/passes/fusion_pass.py:332-333, and the GEMM then runs in a library):
-                        a bias is an epilogue, and a lone ``mm`` is the same kernel with an empty program.
+                        a bias is an epilogue, and a lone ``mm`` is the same kernel with an empty program;
+* ``backward_ops``      pointwise ops of backward graphs (``aten.gelu_backward(grad, pre)``) are absorbed
+                        when the chain value is their gradient argument: ``mm -> gelu_backward`` is the
+                        data-gradient GEMM of a Linear -> GELU pair with ``gelu'(pre)`` as its epilogue.
 """
 from __future__ import annotations
 
@@ -36,7 +39,7 @@ from ..fusion_group import FusionGroup
 from ..registry import SupportedOpsRegistry, build_default_registry
 from .graph_cut import split_fusion_group, validate_fusion_group  # noqa: F401  (re-exported)
 from .mutation_safety import is_safe_inplace
-from .topology import (ABSORBABLE_OPS, BARRIER_OPS, GLOBAL_REDUCTION_OPS, INPLACE_OPS, REDUCTION_OPS,  # noqa: F401
+from .topology import (ABSORBABLE_OPS, BACKWARD_ABSORBABLE_OPS, BARRIER_OPS, GLOBAL_REDUCTION_OPS, INPLACE_OPS, REDUCTION_OPS,  # noqa: F401
                        TRANSPARENT_OPS, TRIGGER_OPS, NodeRole, classify_node, gemm_roofline,
                        RESHAPE_OPS, is_compute_bound_gemm, is_trigger, reduction_axis_code,
                        resolve_through_reshapes, resolve_to_defining_node, symint_safe_eq, symint_safe_len)
@@ -108,13 +111,14 @@ class FuseMLFusionPass:
 
     def __init__(self, graph_module: torch.fx.GraphModule, registry: SupportedOpsRegistry | None = None, *,
                  dag_epilogue: bool = False, multi_reduction: bool = False, global_reductions: bool = False,
-                 bare_trigger: bool = False) -> None:
+                 bare_trigger: bool = False, backward_ops: bool = False) -> None:
         self.graph_module = graph_module
         self.registry = registry or build_default_registry()
         self.dag_epilogue = dag_epilogue
         self.multi_reduction = multi_reduction
         self.global_reductions = global_reductions
         self.bare_trigger = bare_trigger
+        self.backward_ops = backward_ops
 
     # ------------------------------------------------------------------ discovery
     def _find_fusion_groups(self) -> list[FusionGroup]:
@@ -167,6 +171,10 @@ class FuseMLFusionPass:
             if role is NodeRole.UNKNOWN and self.global_reductions and nxt.op == "call_function" \
                     and nxt.target in GLOBAL_REDUCTION_OPS:
                 role = NodeRole.REDUCTION
+            if role is NodeRole.UNKNOWN and self.backward_ops and nxt.op == "call_function" \
+                    and nxt.target in BACKWARD_ABSORBABLE_OPS and nxt.args and nxt.args[0] is cur \
+                    and all(a is not cur for a in nxt.args[1:]):
+                role = NodeRole.ABSORBABLE
             if role in (NodeRole.UNKNOWN, NodeRole.BARRIER):
                 break
             if role is NodeRole.REDUCTION:

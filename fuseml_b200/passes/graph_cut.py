@@ -34,6 +34,7 @@ SUPPORTED_EPILOGUE_OPS: dict[Any, str] = {
     _aten.add_.Tensor: "elementwise",
     _aten.mul.Tensor: "elementwise",
     _aten.mul_.Tensor: "elementwise",
+    _aten.gelu_backward.default: "elementwise",   # absorbed only when discovery runs with backward_ops=True
     _aten.sum.dim_IntList: "reduction",
     _aten.amax.default: "reduction",
     _aten.mean.dim: "reduction",

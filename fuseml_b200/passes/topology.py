@@ -45,6 +45,11 @@ ABSORBABLE_OPS: set[Callable] = {
     _aten.relu.default, _aten.gelu.default, _aten.sigmoid.default, _aten.add.Tensor, _aten.mul.Tensor,
 }
 
+# Pointwise ops of backward graphs whose first argument is the incoming gradient (the chain value)
+# and whose other tensor argument is a saved activation: absorbed only when the pass is asked to
+# (backward_ops=True); the forward-only default set above stays what the reference's is.
+BACKWARD_ABSORBABLE_OPS: set[Callable] = {_aten.gelu_backward.default}
+
 REDUCTION_OPS: set[Callable] = {_aten.sum.dim_IntList, _aten.amax.default, _aten.mean.dim}
 
 # Whole-tensor reductions: only fused when the pass is asked to (global_reductions=True).

@@ -305,3 +305,49 @@ def test_compiled_forward_replays_from_a_cuda_graph(native_lib):
         ref0, ref1 = compiled(args[0]), compiled(new_x)
     assert torch.equal(y0, ref0) and torch.equal(y1, ref1) and not torch.equal(y0, y1)
     torch._dynamo.reset()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_training_step_runs_fused_forward_and_backward(native_lib, dtype):
+    """Forward and backward of the residual MLP block through the compiler.  The forward graph of a
+    training step keeps the pre-activation for the backward pass (an escape store of the first
+    kernel); the backward graph becomes four fused launches: the data-gradient GEMM with
+    gelu'(pre) as its epilogue, the data-gradient GEMM with the residual's gradient added, and
+    the two weight-gradient GEMMs dY^T @ X, whose transposed left operand is read in place.
+    Gradients are compared with fp32 autograd on the same (rounded) parameters."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+
+    td = {"bf16": torch.bfloat16, "f32": torch.float32}[dtype]
+    torch._dynamo.reset()
+    case = configs.make("cfg4", small=True)                   # 136 tokens, 128 -> 520 -> 128
+    model = case.module.to(device="cuda", dtype=td)
+    ref_model = configs.make("cfg4", small=True).module.to(device="cuda", dtype=torch.float32)
+    with torch.no_grad():
+        for p_ref, p in zip(ref_model.parameters(), model.parameters()):
+            p_ref.copy_(p.float())
+    x = case.args[0].to(device="cuda", dtype=td).requires_grad_(True)
+    x_ref = x.detach().float().requires_grad_(True)
+    w = torch.randn(x.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+
+    comp = F.FuseMLCompiler()
+    y = torch.compile(model, backend=comp)(x)
+    (y.float() * w).sum().backward()
+    y_ref = ref_model(x_ref)
+    (y_ref * w).sum().backward()
+    torch.cuda.synchronize()
+    assert F.device_status() == 0
+    assert comp.fusion_applied and len(comp.launchers) == 6 and len(comp.backward_launchers) == 4, comp.declined
+    assert all(L.launch_count == 1 for L in comp.launchers)
+    tol = dict(rtol=3e-2, atol=3e-2) if dtype == "bf16" else dict(rtol=2e-3, atol=2e-3)
+
+    def close(got, ref, what):
+        scale = float(ref.abs().max())
+        np.testing.assert_allclose(got.float().cpu().numpy() / scale, ref.cpu().numpy() / scale, err_msg=what, **tol)
+
+    close(y.detach(), y_ref.detach(), "y")
+    close(x.grad, x_ref.grad, "dx")
+    for (name, p), p_ref in zip(model.named_parameters(), ref_model.parameters()):
+        close(p.grad, p_ref.grad, f"d{name}")
+    torch._dynamo.reset()

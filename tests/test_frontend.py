@@ -301,3 +301,39 @@ def test_plan_cache_round_trip_and_candidates(tmp_path):
     # 8192 rows: 27.7 waves, nothing to gain from narrower tiles; only the group size varies
     full = pc.candidate_plans(base, 8192, 16384)
     assert {c.tile_n for c in full} == {256} and len(full) == 3
+
+
+def test_backward_graph_lowers_to_four_fused_gemms():
+    """The backward graph AOT autograd builds for ``l2(gelu(l1(x))) + x`` (written out with ATen ops):
+    with the backward extensions on, the data-gradient GEMM absorbs ``gelu_backward`` (the saved
+    pre-activation becomes an epilogue operand), the other one absorbs the residual's gradient, and
+    the two weight-gradient GEMMs (transposed-view left operand) are bare triggers."""
+    aten = torch.ops.aten
+
+    def bw(x, t, addmm, gelu, t_1, tang):
+        mm = aten.mm(tang, aten.t(t_1))
+        mm_1 = aten.mm(aten.t(tang), gelu)
+        gb = aten.gelu_backward(mm, addmm)
+        mm_2 = aten.mm(gb, aten.t(t))
+        mm_3 = aten.mm(aten.t(gb), x)
+        return aten.t(mm_3), aten.sum.dim_IntList(gb, [0], True), aten.add.Tensor(tang, mm_2), aten.t(mm_1)
+
+    M, D, I = 32, 64, 256
+    args = (torch.randn(M, D), torch.randn(I, D).t(), torch.randn(M, I), torch.randn(M, I), torch.randn(D, I).t(),
+            torch.randn(M, D))
+    gm = make_fx(bw)(*args)
+    ShapeProp(gm).propagate(*args)
+    assert F.FuseMLFusionPass(gm)._find_fusion_groups()[0].op_signature == ("aten.mm.default", "aten.add.Tensor")
+    F.FuseMLFusionPass(gm, bare_trigger=True, backward_ops=True).run()
+    lowered = sorted(([N.OP_NAMES[s.opcode] for s in spec.steps], len(g.inputs)) for g, spec in _specs(gm))
+    assert lowered == [([], 2), ([], 2), (["add_t"], 3), (["gelu_erf_bwd_t"], 3)]
+    # gelu_backward of the tanh form has no epilogue op: the chain is declined, not mis-lowered
+    def bw_tanh(tang, w, pre):
+        return aten.gelu_backward(aten.mm(tang, w), pre, approximate="tanh")
+    args = (torch.randn(8, 16), torch.randn(16, 8), torch.randn(8, 8))
+    gm = make_fx(bw_tanh)(*args)
+    ShapeProp(gm).propagate(*args)
+    F.FuseMLFusionPass(gm, backward_ops=True).run()
+    g = next(n.meta["fusion_group"] for n in gm.graph.nodes if n.meta.get("fusion_group") is not None)
+    with pytest.raises(UnsupportedChainError):
+        Sm100KernelGenerator().build_spec(g)
