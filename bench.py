@@ -49,7 +49,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # mean of its two launches (first GEMM 0.671 GB, second GEMM 1.779 GB: with K = 16384 the operand
 # slabs of one wave of tiles do not survive in L2 until the next wave; algorithmic bytes are
 # 0.47 GB per launch).  cfg5 was not captured (the same two kernels as cfg4, four times).
-NCU_TRAFFIC_BYTES = {"cfg1": None, "cfg4": 1.2248e9, "cfg2": 1.483e8, "cfg3": 1.504e8, "cfg5": None}
+NCU_TRAFFIC_BYTES = {"cfg1": None, "cfg4": 1.2248e9, "cfg2": 1.483e8, "cfg3": 1.504e8, "cfg5": None,
+                     "cfg4_training_step": None}
 
 
 def load_peaks():
@@ -402,6 +403,34 @@ class SmallFp32MLP(Workload):
         torch.cuda.current_stream().synchronize()
 
 
+class TrainingStep(Workload):
+    """Forward and backward of the cfg4 block through the compiler: two fused forward kernels (the
+    first also stores the pre-activation for the backward pass) and four fused backward GEMMs
+    (data gradients with gelu'(pre) / the residual's gradient as epilogues, weight gradients with
+    the transposed operand read in place).  Six GEMMs of 2*M*D*I FLOP each per step."""
+
+    name = "cfg4_training_step"
+    bound = "tensor"
+    expected_kernels = 6
+
+    def __init__(self, rows=8192, d_model=4096, d_inter=16384, seed=0):
+        torch.manual_seed(seed)
+        self._compile(TransformerMLP(d_model, d_inter).to(device="cuda", dtype=torch.bfloat16))
+        self.module.train()
+        self.x = torch.randn(rows, d_model, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        self.dy = torch.randn(rows, d_model, device="cuda", dtype=torch.bfloat16)
+        self.tokens = rows
+        self.flops_per_launch = 2.0 * rows * d_model * d_inter
+        self.flops = 6 * self.flops_per_launch
+        self.launches_per_step = self.gemm_launches_per_step = 6
+
+    def step(self):
+        for p in self.module.parameters():
+            p.grad = None
+        self.x.grad = None
+        self.compiled(self.x).backward(self.dy)
+
+
 def make_workload(name, world, scaling):
     if name == "cfg1":
         return SmallFp32MLP()
@@ -725,9 +754,13 @@ def measure(h, wl, name, W, steps, use_graph, peaks, peak_src, world, sustained_
 
 def measure_e2e(h, wl, steps, world):
     ceiling_ms = link_ceiling(h, wl, steps)
-    for _ in range(2):
+    # warm-up: the three-stream pipeline keeps several steps' outputs alive at once; the caching
+    # allocator must have grown to that depth before the timed region (a cudaMalloc inside it
+    # synchronises the device and stalls the pipeline)
+    for _ in range(8):
         wl.e2e_step()
     wl.e2e_finish()
+    torch.cuda.synchronize()
     e2e_ms, _ = h.timed(wl.e2e_step, steps, finish=wl.e2e_finish, clocks=False)
     per = e2e_ms / steps
     moved = (wl.h2d_bytes + wl.d2h_bytes) * world
@@ -839,6 +872,14 @@ def main():
                 rec["allreduce"] = {"ms_per_call": ar_ms / 200, "calls_per_step": 1, "inside_timed_region": True,
                                     "what": "NCCL all-reduce of the global sum (SUM) and amax (MAX), 4 bytes each"}
             extras[other] = rec
+            wl = None
+            release()
+        if world == 1 and name == "cfg4":
+            wl = TrainingStep()
+            m = measure(h, wl, "cfg4_training_step", 3, 5, False, peaks, peak_src, world)
+            extras["cfg4_training_step"] = {"what": "forward + backward of the cfg4 block, six fused GEMMs, bf16",
+                                            "burst": {k: m[k] for k in ("ms_per_step", "steps", "tokens_per_s", "roofline")},
+                                            **m["sustained"]}
             wl = None
             release()
 

@@ -39,15 +39,29 @@ __global__ void __launch_bounds__(256) splitk_finish_kernel(const __grid_constan
   float v[kFinishChunk];
 #pragma unroll
   for (int i = 0; i < kFinishChunk; ++i) v[i] = 0.0f;
-  for (int s = 0; s < p.split_k; ++s) {
-    const float4* q = src + s * (slice_floats / 4);
+  // Four slices' loads are issued before the first is added (sixteen 16-byte loads in flight per
+  // thread: the pass is bound by load latency, not bandwidth); the additions keep slice order.
+  constexpr int kBatch = 4;
+  for (int s0 = 0; s0 < p.split_k; s0 += kBatch) {
+    float4 x[kBatch][kFinishChunk / 4];
 #pragma unroll
-    for (int i = 0; i < kFinishChunk / 4; ++i) {
-      const float4 x = __ldcs(q + i * kTileM);   // read once: do not keep the partials in cache
-      v[4 * i + 0] += x.x;
-      v[4 * i + 1] += x.y;
-      v[4 * i + 2] += x.z;
-      v[4 * i + 3] += x.w;
+    for (int u = 0; u < kBatch; ++u) {
+      const float4* q = src + static_cast<int64_t>(s0 + u) * (slice_floats / 4);
+#pragma unroll
+      for (int i = 0; i < kFinishChunk / 4; ++i)
+        x[u][i] = (s0 + u < p.split_k) ? __ldcs(q + i * kTileM) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);   // read once
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      if (s0 + u < p.split_k) {
+#pragma unroll
+        for (int i = 0; i < kFinishChunk / 4; ++i) {
+          v[4 * i + 0] += x[u][i].x;
+          v[4 * i + 1] += x[u][i].y;
+          v[4 * i + 2] += x[u][i].z;
+          v[4 * i + 3] += x[u][i].w;
+        }
+      }
     }
   }
   epi::run_program<USES_SAVED ? epi::kProgGenericSaved : epi::kProgGeneric, kFinishChunk>(p, m, n0, true, v, nullptr, 0);
