@@ -39,6 +39,7 @@ OP_NAMES = {
 # reductions ---------------------------------------------------------------------
 RED_SUM, RED_MAX, RED_MEAN = 1, 2, 4
 PLAN_B_EXPANSION_VALID = 1
+MLP_WEIGHTS_EXPANDED = 1
 WHERE_MMA_FULL = 0x202
 AXIS_M, AXIS_N, AXIS_ALL = 0, 1, 2
 
@@ -73,6 +74,21 @@ class GemmDesc(C.Structure):
     ]
 
 
+class MlpDesc(C.Structure):
+    _fields_ = [
+        ("M", C.c_int64), ("D_in", C.c_int64), ("I", C.c_int64), ("D_out", C.c_int64),
+        ("x", C.c_void_p), ("ldx", C.c_int64),
+        ("w1", C.c_void_p), ("ldw1", C.c_int64),
+        ("w2", C.c_void_p), ("ldw2", C.c_int64),
+        ("ab_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("y", C.c_void_p), ("ldy", C.c_int64),
+        ("n_ops1", C.c_int32), ("n_ops2", C.c_int32), ("n_operands", C.c_int32), ("flags", C.c_int32),
+        ("ops1", EpiOp * MAX_EPI_OPS), ("ops2", EpiOp * MAX_EPI_OPS),
+        ("operands", Operand * MAX_OPERANDS),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+    ]
+
+
 class Plan(C.Structure):
     _fields_ = [
         ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32), ("stages", C.c_int32),
@@ -101,7 +117,7 @@ EXPORTS = (
     "fuseml_sm100_gemm_epilogue", "fuseml_sm100_reduce_tail", "fuseml_sm100_device_status",
     "fuseml_sm100_strerror", "fuseml_sm100_abi_version",
     "fuseml_sm100_gemm_epilogue_noalloc", "fuseml_sm100_noalloc_scratch_bytes",
-    "fuseml_sm100_set_diagnostics",
+    "fuseml_sm100_set_diagnostics", "fuseml_sm100_mlp_small", "fuseml_sm100_mlp_small_workspace_bytes",
 )
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfuseml_sm100.so"
@@ -136,6 +152,10 @@ def _declare(lib: C.CDLL) -> None:
     lib.fuseml_sm100_reduce_tail.restype = C.c_int
     lib.fuseml_sm100_reduce_tail.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
                                              C.POINTER(Reduce), C.c_void_p]
+    lib.fuseml_sm100_mlp_small.restype = C.c_int
+    lib.fuseml_sm100_mlp_small.argtypes = [C.POINTER(MlpDesc), C.c_void_p]
+    lib.fuseml_sm100_mlp_small_workspace_bytes.restype = C.c_int64
+    lib.fuseml_sm100_mlp_small_workspace_bytes.argtypes = [C.POINTER(MlpDesc)]
     lib.fuseml_sm100_set_diagnostics.restype = C.c_int
     lib.fuseml_sm100_set_diagnostics.argtypes = [C.c_int64, C.c_int32]
     lib.fuseml_sm100_device_status.restype = C.c_int

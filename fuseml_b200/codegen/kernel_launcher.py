@@ -432,3 +432,75 @@ class KernelLauncher:
         blk = f"block=({lp.block_m},{lp.block_n},{lp.block_k})" if lp is not None else "block=(router)"
         return (f"KernelLauncher(inputs={ins}, output={self._output_descriptor.name!r}, "
                 f"intermediates={[d.name for d in self._intermediate_descriptors]}, {blk}{red})")
+
+
+class FusedMLPLauncher:
+    """Two chained launchers, ``h = first(...)`` and ``y = second(..., h, ...)``, run as ONE kernel
+    when the batch has at most 128 rows: ``fuseml_sm100_mlp_small`` computes both Linears with the
+    intermediate handed over in shared memory (decode-sized batches, small fp32 blocks).  Any other
+    call (more rows, a layout the kernel does not take) runs the two fused launches one after the
+    other, exactly as the graph did before the pair was merged.
+
+    Inputs: the first launcher's inputs followed by the second's without its left operand.
+    The reference has no counterpart: its two Linears are always two kernels with ``h`` in HBM
+    (benchmarks/bench_mlp_block.py:160-182)."""
+
+    def __init__(self, first: KernelLauncher, second: KernelLauncher) -> None:
+        self.__name__ = "fuseml_fused_mlp"
+        self.first, self.second = first, second
+        self._n1 = len(first._input_descriptors)
+        self._pos = second._left_idx                       # where h sits among the second launcher's inputs
+        self._ws: dict = {}
+        self._declined: set = set()
+        self.fused_count = 0
+        self.launch_count = 0
+
+    @staticmethod
+    def mergeable(first: KernelLauncher, second: KernelLauncher) -> bool:
+        """Static conditions: plain stored outputs, no reductions, no escape stores on either side."""
+        for L in (first, second):
+            sp = L._spec
+            if sp.reductions or sp.n_aux or not sp.store_output or L._aux_slots:
+                return False
+        return first._output_descriptor.dtype == first._input_descriptors[first._left_idx].dtype
+
+    @staticmethod
+    def _program(launcher: KernelLauncher, inputs: Sequence[torch.Tensor]) -> K.EpilogueProgram:
+        prog = K.EpilogueProgram()
+        for st in launcher._spec.steps:
+            if st.input_index >= 0:
+                prog.ops.append((st.opcode, prog._slot(inputs[st.input_index]), 0.0))
+            else:
+                prog.ops.append((st.opcode, 0, st.imm))
+        return prog
+
+    def __call__(self, *tensors: torch.Tensor):
+        a1 = tensors[:self._n1]
+        rest = tensors[self._n1:]
+        x, w1v = a1[self.first._left_idx], a1[self.first._right_idx]
+        w2v = rest[self.second._right_idx - (1 if self.second._right_idx > self._pos else 0)]
+        key = (x.shape, x.stride(), w1v.stride(), w2v.shape, w2v.stride(), x.dtype)
+        # nn.Linear weights reach the launchers as aten.t views: stride (1, K) means the storage is [N, K] row-major
+        fusable = (key not in self._declined and x.dim() == 2 and x.shape[0] <= 128 and x.stride(1) == 1
+                   and w1v.dim() == 2 and w2v.dim() == 2 and w1v.stride(0) == 1 and w2v.stride(0) == 1)
+        if fusable:
+            a2 = list(rest)
+            a2.insert(self._pos, None)                      # h has no tensor in the fused form
+            try:
+                stream = torch.cuda.current_stream(x.device).cuda_stream
+                ws = self._ws.get((key, stream))
+                y = K.fused_mlp(x, w1v.t(), w2v.t(), self._program(self.first, a1), self._program(self.second, a2),
+                                out_dtype=self.second._output_descriptor.dtype, workspace=ws)
+                if ws is None:
+                    self._ws[(key, stream)] = K.last_mlp_workspace()
+                self.fused_count += 1
+                self.launch_count += 1
+                return y
+            except N.NativeLibraryError as exc:
+                self._declined.add(key)
+                logger.info("MLP block runs as two launches: %s", exc)
+        h = self.first(*a1)
+        a2 = list(rest)
+        a2.insert(self._pos, h)
+        self.launch_count += 1
+        return self.second(*a2)

@@ -90,7 +90,8 @@ class FuseMLCompiler:
 
     def __init__(self, registry: SupportedOpsRegistry | None = None, *, dag_epilogue: bool = True,
                  multi_reduction: bool = True, global_reductions: bool = True, bare_trigger: bool = True,
-                 backward: bool = True, plan_cache: Any = None, autotune: bool | None = None) -> None:
+                 backward: bool = True, fuse_mlp: bool = True, plan_cache: Any = None,
+                 autotune: bool | None = None) -> None:
         self.registry: SupportedOpsRegistry = registry or build_default_registry()
         self.fusion_candidates: list = []
         self.fusion_applied: bool = False
@@ -101,6 +102,10 @@ class FuseMLCompiler:
         # fuseml/compiler.py:214-218)
         self.backward_launchers: list[KernelLauncher] = []
         self.fuse_backward = bool(backward)
+        # pairs of chained launchers merged into one call that runs both Linears in one kernel when
+        # the batch has at most 128 rows (FusedMLPLauncher); `fuse_mlp=False` keeps them separate
+        self.mlp_launchers: list = []
+        self.fuse_mlp = bool(fuse_mlp)
         self.declined: list[tuple[str, str]] = []
         self._options = dict(dag_epilogue=dag_epilogue, multi_reduction=multi_reduction,
                              global_reductions=global_reductions, bare_trigger=bare_trigger, backward_ops=True)
@@ -205,6 +210,8 @@ class FuseMLCompiler:
                 call.meta.update({k: v for k, v in node.meta.items() if k in ("tensor_meta", "val", "fusion_group")})
                 node.replace_all_uses_with(call)
                 graph.erase_node(node)
+        if self.fuse_mlp:
+            self._merge_mlp_pairs(graph)
         graph.eliminate_dead_code()
         graph.lint()
         gm.recompile()
@@ -212,6 +219,35 @@ class FuseMLCompiler:
         self.fusion_strategy = "sm100"
         logger.info("FuseML: %d fused kernel(s) in graph (%d declined)", len(accepted), len(self.declined))
         return gm.forward
+
+    def _merge_mlp_pairs(self, graph: torch.fx.Graph) -> None:
+        """``second(..., first(...), ...)`` with the first launcher's output feeding only the second's
+        left operand, plain stored outputs on both sides and at most 128 rows: one FusedMLPLauncher."""
+        from .codegen.kernel_launcher import FusedMLPLauncher
+
+        for node in list(graph.nodes):
+            if node.op != "call_function" or not isinstance(node.target, KernelLauncher):
+                continue
+            second = node.target
+            left = node.args[second._left_idx]
+            if not (isinstance(left, torch.fx.Node) and left.op == "call_function" and isinstance(left.target, KernelLauncher)):
+                continue
+            first = left.target
+            if len(left.users) != 1 or sum(1 for a in node.args if a is left) != 1:
+                continue
+            rows_shape = first._input_descriptors[first._left_idx].shape
+            if len(rows_shape) != 2 or rows_shape[0] > 128 or not FusedMLPLauncher.mergeable(first, second):
+                continue
+            merged = FusedMLPLauncher(first, second)
+            args = tuple(left.args) + tuple(a for i, a in enumerate(node.args) if i != second._left_idx)
+            with graph.inserting_after(node):
+                call = graph.call_function(merged, args=args)
+            call.meta.update({k: v for k, v in node.meta.items() if k in ("tensor_meta", "val")})
+            node.replace_all_uses_with(call)
+            graph.erase_node(node)
+            graph.erase_node(left)
+            self.mlp_launchers.append(merged)
+            logger.info("merged %s and %s into one small-M MLP launch", first, second)
 
     # ------------------------------------------------------------------ helpers
     @staticmethod

@@ -175,11 +175,12 @@ struct SplitJob {
   int32_t blocks;      // blocks of the launch that work on this job (0 = none)
 };
 
-// Both operands in one launch: blocks [0, a.blocks) expand A, the rest expand B.
-__global__ void split_tf32_kernel(const SplitJob a, const SplitJob b) {
-  const bool first = static_cast<int32_t>(blockIdx.x) < a.blocks;
-  const SplitJob& j = first ? a : b;
-  const int64_t block = first ? blockIdx.x : blockIdx.x - a.blocks;
+// Up to three operands in one launch: blocks [0, a.blocks) expand a, the next b.blocks expand b,
+// the rest c (a job with blocks == 0 is skipped).
+__global__ void split_tf32_kernel(const SplitJob a, const SplitJob b, const SplitJob c) {
+  const int32_t bx = static_cast<int32_t>(blockIdx.x);
+  const SplitJob& j = bx < a.blocks ? a : (bx < a.blocks + b.blocks ? b : c);
+  const int64_t block = bx < a.blocks ? bx : (bx < a.blocks + b.blocks ? bx - a.blocks : bx - a.blocks - b.blocks);
   const int64_t total = j.rows * j.K;
   for (int64_t i = block * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(j.blocks) * blockDim.x) {

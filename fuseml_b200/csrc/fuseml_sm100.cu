@@ -8,11 +8,13 @@
 #include <cstdint>
 #include <atomic>
 #include <cstring>
+#include <initializer_list>
 #include <mutex>
 
 #include "../../include/fuseml_sm100.h"
 #include "aux_kernels.cuh"
 #include "gemm_kernel_v2.cuh"
+#include "mlp_small_kernel.cuh"
 #include "splitk_finish.cuh"
 #include "host_plan.h"
 
@@ -344,7 +346,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
                    static_cast<int32_t>(std::min<int64_t>((tb + threads - 1) / threads, 148 * 8))};
     if (plan.flags & FUSEML_PLAN_B_EXPANSION_VALID) jb.blocks = 0;
     // one launch for both operands
-    split_tf32_kernel<<<ja.blocks + jb.blocks, threads, 0, stream>>>(ja, jb);
+    SplitJob none = {};
+    split_tf32_kernel<<<ja.blocks + jb.blocks, threads, 0, stream>>>(ja, jb, none);
     if (cudaGetLastError() != cudaSuccess) return FUSEML_E_LAUNCH;
     a_ptr = a2; b_ptr = b2; K = 3 * desc->K; lda = ld; ldb = ld; b_mn = false; a_mn = false;
   }
@@ -511,6 +514,218 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     rc = run_finalize(desc->reduce, w, ws, count, stream);
   }
   return rc;
+}
+
+// ---- small-M MLP block in one kernel --------------------------------------------------------
+namespace fuseml {
+
+struct MlpLayout {
+  int32_t bi, groups, n_dchunks, slices;
+  int64_t x_off, w1_off, w2_off, part_off, total;   // workspace (the first three: fp32 expansions)
+  int64_t ld1, ld2;                                 // leading dimensions of the expansions
+};
+
+static bool mlp_uses(const fuseml_epi_op_t* ops, int n, std::initializer_list<int32_t> codes) {
+  for (int i = 0; i < n; ++i)
+    for (int32_t c : codes)
+      if (ops[i].opcode == c) return true;
+  return false;
+}
+
+// FUSEML_OK and the layout, or the reason the block cannot run as one kernel.
+static int mlp_layout(const fuseml_mlp_desc_t* d, MlpLayout* L) {
+  if (d == nullptr) return FUSEML_E_NULL;
+  if (d->x == nullptr || d->w1 == nullptr || d->w2 == nullptr || d->y == nullptr) return FUSEML_E_NULL;
+  if (d->M <= 0 || d->D_in <= 0 || d->I <= 0 || d->D_out <= 0) return FUSEML_E_SHAPE;
+  if (d->M > 128 || d->D_in > (1 << 24) || d->I > (1 << 24) || d->D_out > (1 << 24)) return FUSEML_E_SHAPE;
+  const int eb = dtype_bytes(d->ab_dtype);
+  if (eb == 0 || dtype_bytes(d->out_dtype) == 0) return FUSEML_E_DTYPE;
+  const bool f32 = d->ab_dtype == FUSEML_F32;
+  if (d->ldx < d->D_in || d->ldw1 < d->D_in || d->ldw2 < d->I || d->ldy < d->D_out) return FUSEML_E_LAYOUT;
+  if (!f32) {
+    for (const void* p : {d->x, d->w1, d->w2})
+      if (reinterpret_cast<uintptr_t>(p) & 15u) return FUSEML_E_LAYOUT;
+    if ((d->ldx * eb) % 16 || (d->ldw1 * eb) % 16 || (d->ldw2 * eb) % 16) return FUSEML_E_LAYOUT;
+  } else if (d->I % 4 != 0) {
+    return FUSEML_E_LAYOUT;             // the three copies of an expanded row must start on 16-byte boundaries
+  }
+  if (d->n_ops1 < 0 || d->n_ops1 > FUSEML_MAX_EPI_OPS || d->n_ops2 < 0 || d->n_ops2 > FUSEML_MAX_EPI_OPS ||
+      d->n_operands < 0 || d->n_operands > FUSEML_MAX_OPERANDS)
+    return FUSEML_E_EPILOGUE;
+  for (int pass = 0; pass < 2; ++pass) {
+    const fuseml_epi_op_t* ops = pass ? d->ops2 : d->ops1;
+    const int n = pass ? d->n_ops2 : d->n_ops1;
+    for (int i = 0; i < n; ++i) {
+      const int32_t oc = ops[i].opcode;
+      if (oc < 0 || oc >= FUSEML_OP__COUNT) return FUSEML_E_EPILOGUE;
+      const bool uses = oc == FUSEML_OP_ADD_T || oc == FUSEML_OP_MUL_T || oc == FUSEML_OP_SUB_T || oc == FUSEML_OP_RSUB_T ||
+                        oc == FUSEML_OP_STORE_AUX || oc == FUSEML_OP_GELU_ERF_BWD_T;
+      if (uses) {
+        if (ops[i].slot < 0 || ops[i].slot >= d->n_operands) return FUSEML_E_EPILOGUE;
+        const fuseml_operand_t& o = d->operands[ops[i].slot];
+        if (o.ptr == nullptr) return FUSEML_E_NULL;
+        if (dtype_bytes(o.dtype) == 0) return FUSEML_E_DTYPE;
+        if (o.stride_m < 0 || o.stride_n < 0) return FUSEML_E_LAYOUT;
+      }
+    }
+  }
+  // the first program runs in the interpreter without the second register and without escape stores
+  fuseml_epi_op_t tmp[FUSEML_MAX_EPI_OPS];
+  const int n1 = fuse_diamonds(d->ops1, d->n_ops1, tmp);
+  if (mlp_uses(tmp, n1, {FUSEML_OP_SAVE, FUSEML_OP_SWAP, FUSEML_OP_ADD_SAVED, FUSEML_OP_MUL_SAVED, FUSEML_OP_STORE_AUX}))
+    return FUSEML_E_EPILOGUE;
+  // slice width: the widest of the candidates that divides I
+  const int cands[2] = {f32 ? 64 : 128, f32 ? 32 : 64};
+  int bi = 0;
+  for (int c : cands)
+    if (bi == 0 && d->I % c == 0) bi = c;
+  if (bi == 0) return FUSEML_E_SHAPE;
+  L->bi = bi;
+  L->slices = static_cast<int32_t>(d->I / bi);
+  L->n_dchunks = static_cast<int32_t>((d->D_out + 255) / 256);
+  // CTAs per output chunk: one per slice if they fit the machine; the partial tiles (128 KB per CTA) stay within 8 MiB
+  const int per_chunk = std::max(1, std::min(148, 64) / L->n_dchunks);
+  L->groups = std::max(1, std::min(L->slices, per_chunk));
+  if (static_cast<int64_t>(L->groups) * L->n_dchunks > 148) return FUSEML_E_SHAPE;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) { const int64_t at = off; off += (bytes + 255) / 256 * 256; return at; };
+  L->ld1 = split_ld(d->D_in);
+  L->ld2 = split_ld(d->I);
+  L->x_off = L->w1_off = L->w2_off = 0;
+  if (f32) {
+    L->x_off = take(d->M * L->ld1 * 4);
+    L->w1_off = take(d->I * L->ld1 * 4);
+    L->w2_off = take(d->D_out * L->ld2 * 4);
+  }
+  L->part_off = take(static_cast<int64_t>(L->groups) * L->n_dchunks * 128 * 256 * 4);
+  L->total = off;
+  return FUSEML_OK;
+}
+
+}  // namespace fuseml
+
+int64_t fuseml_sm100_mlp_small_workspace_bytes(const fuseml_mlp_desc_t* desc) {
+  MlpLayout L;
+  return mlp_layout(desc, &L) == FUSEML_OK ? L.total : -1;
+}
+
+int fuseml_sm100_mlp_small(const fuseml_mlp_desc_t* desc, void* cuda_stream) {
+  MlpLayout L;
+  int rc = mlp_layout(desc, &L);
+  if (rc != FUSEML_OK) return rc;
+  char* ws = reinterpret_cast<char*>(desc->workspace);
+  if (ws == nullptr || desc->workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(ws) & 15u)) return FUSEML_E_WORKSPACE;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  const bool f32 = desc->ab_dtype == FUSEML_F32;
+  const int fmt = f32 ? 2 : (desc->ab_dtype == FUSEML_BF16 ? 1 : 0);
+  const int BK = f32 ? 32 : 64;
+
+  const void* x = desc->x; const void* w1 = desc->w1; const void* w2 = desc->w2;
+  int64_t K1 = desc->D_in, K2 = desc->I, ldx = desc->ldx, ldw1 = desc->ldw1, ldw2 = desc->ldw2;
+  if (f32) {
+    float* xe = reinterpret_cast<float*>(ws + L.x_off);
+    float* w1e = reinterpret_cast<float*>(ws + L.w1_off);
+    float* w2e = reinterpret_cast<float*>(ws + L.w2_off);
+    const int threads = 256;
+    auto blocks = [&](int64_t n) { return static_cast<int32_t>(std::min<int64_t>((n + threads - 1) / threads, 148 * 8)); };
+    SplitJob jx = {reinterpret_cast<const float*>(desc->x), desc->M, desc->D_in, desc->ldx, 1, 0, xe, L.ld1, blocks(desc->M * desc->D_in)};
+    SplitJob j1 = {reinterpret_cast<const float*>(desc->w1), desc->I, desc->D_in, desc->ldw1, 1, 1, w1e, L.ld1, blocks(desc->I * desc->D_in)};
+    SplitJob j2 = {reinterpret_cast<const float*>(desc->w2), desc->D_out, desc->I, desc->ldw2, 1, 1, w2e, L.ld2, blocks(desc->D_out * desc->I)};
+    if (desc->flags & FUSEML_MLP_WEIGHTS_EXPANDED) j1.blocks = j2.blocks = 0;
+    split_tf32_kernel<<<jx.blocks + j1.blocks + j2.blocks, threads, 0, stream>>>(jx, j1, j2);
+    if (cudaGetLastError() != cudaSuccess) return FUSEML_E_LAUNCH;
+    x = xe; w1 = w1e; w2 = w2e; K1 = 3 * desc->D_in; K2 = 3 * desc->I; ldx = ldw1 = L.ld1; ldw2 = L.ld2;
+  }
+  CUtensorMap tx, t1, t2;
+  if ((rc = encode_2d(&tx, desc->ab_dtype, x, desc->M, K1, ldx, BK, 128)) != FUSEML_OK) return rc;
+  if ((rc = encode_2d(&t1, desc->ab_dtype, w1, desc->I, K1, ldw1, BK, L.bi)) != FUSEML_OK) return rc;
+  if ((rc = encode_2d(&t2, desc->ab_dtype, w2, desc->D_out, K2, ldw2, BK, 256)) != FUSEML_OK) return rc;
+
+  void* status_ptr = nullptr;
+  if (cudaGetSymbolAddress(&status_ptr, g_status_word) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
+
+  mlp::MlpParams q;
+  std::memset(&q, 0, sizeof(q));
+  q.M = static_cast<int32_t>(desc->M);
+  q.I = static_cast<int32_t>(desc->I);
+  q.D_out = static_cast<int32_t>(desc->D_out);
+  q.fmt = fmt;
+  q.bi = L.bi;
+  q.num_slices = L.slices;
+  q.groups = L.groups;
+  q.n_dchunks = L.n_dchunks;
+  q.kb1 = static_cast<int32_t>((K1 + BK - 1) / BK);
+  q.out16 = desc->ab_dtype == FUSEML_F16 ? 1 : 0;
+  q.split_ws = reinterpret_cast<float*>(ws + L.part_off);
+  q.status = reinterpret_cast<int32_t*>(status_ptr);
+  q.wait_limit_us = g_diag_wait_limit_us.load(std::memory_order_relaxed);
+
+  // program 1 runs on h[M, I]; program 2 (in the finish pass) on y[M, D_out]
+  GemmParams p1, p2;
+  std::memset(&p1, 0, sizeof(p1));
+  std::memset(&p2, 0, sizeof(p2));
+  for (GemmParams* p : {&p1, &p2}) {
+    for (int i = 0; i < desc->n_operands; ++i) {
+      p->operands[i].ptr = desc->operands[i].ptr;
+      p->operands[i].stride_m = desc->operands[i].stride_m;
+      p->operands[i].stride_n = desc->operands[i].stride_n;
+      p->operands[i].dtype = desc->operands[i].dtype;
+    }
+    p->M = q.M;
+    p->vec_slot[0] = p->vec_slot[1] = -1;
+    p->mat_slot = -1;
+    p->status = q.status;
+  }
+  p1.N = q.I;
+  p1.n_ops = fuse_diamonds(desc->ops1, desc->n_ops1, p1.ops);
+  p2.N = q.D_out;
+  p2.n_ops = fuse_diamonds(desc->ops2, desc->n_ops2, p2.ops);
+  for (int i = 0; i < p1.n_ops; ++i) p1.ops[i].reserved = 0;
+  for (int i = 0; i < p2.n_ops; ++i) {
+    p2.ops[i].reserved = 0;
+    const int32_t oc = p2.ops[i].opcode;
+    if (oc == FUSEML_OP_SAVE || oc == FUSEML_OP_SWAP || oc == FUSEML_OP_ADD_SAVED || oc == FUSEML_OP_MUL_SAVED) p2.uses_saved = 1;
+  }
+  p2.tiles_m = 1;
+  p2.tiles_n = p2.num_tiles = L.n_dchunks;
+  p2.group_m = 1;
+  p2.bn = 256;
+  p2.d = desc->y;
+  p2.ldd = desc->ldy;
+  p2.out_dtype = desc->out_dtype;
+  p2.split_k = L.groups;
+  p2.split_ws = q.split_ws;
+
+  {
+    static std::mutex mutex;
+    static bool configured[kMaxDevices] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return FUSEML_E_DEVICE; }
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!configured[dev]) {
+      if (cudaFuncSetAttribute(mlp::mlp_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mlp::kDynamicBytes) != cudaSuccess) {
+        cudaGetLastError();
+        return FUSEML_E_LAUNCH;
+      }
+      configured[dev] = true;
+    }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.gridDim = dim3(L.groups * L.n_dchunks);
+  cfg.blockDim = dim3(mlp::kThreads);
+  cfg.dynamicSmemBytes = mlp::kDynamicBytes;
+  cfg.stream = stream;
+  if (cudaLaunchKernelEx(&cfg, mlp::mlp_small_kernel, tx, t1, t2, q, p1) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_LAUNCH; }
+
+  const int64_t work = static_cast<int64_t>(L.n_dchunks) * kTileM * (256 / kFinishChunk);
+  const int blocks = static_cast<int>((work + 255) / 256);
+  if (p2.uses_saved) splitk_finish_kernel<true><<<blocks, 256, 0, stream>>>(p2);
+  else splitk_finish_kernel<false><<<blocks, 256, 0, stream>>>(p2);
+  return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
 }
 
 int fuseml_sm100_reduce_tail(const void* x, int32_t dtype, int64_t M, int64_t N, int64_t ldx,

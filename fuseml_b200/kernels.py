@@ -298,6 +298,82 @@ def fused_gemm(a: torch.Tensor, b: torch.Tensor, program: EpilogueProgram | None
     return out
 
 
+_last_mlp_workspace: list = [None]
+
+
+def last_mlp_workspace() -> torch.Tensor | None:
+    """The workspace the most recent :func:`fused_mlp` call used (callers that launch the same block
+    again pass it back in instead of allocating a new one)."""
+    return _last_mlp_workspace[0]
+
+
+def fused_mlp(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, prog1: EpilogueProgram | None = None,
+              prog2: EpilogueProgram | None = None, *, out_dtype: torch.dtype | None = None,
+              out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+              weights_expanded: bool = False) -> torch.Tensor:
+    """``prog2(prog1(x @ w1.T) @ w2.T)`` for at most 128 rows in one kernel (plus the pass that folds
+    the CTAs' partial outputs): the intermediate never reaches global memory.  ``w1[I, D_in]`` and
+    ``w2[D_out, I]`` are the ``nn.Linear`` weights as stored.  ``prog1`` sees ``h[M, I]``, ``prog2``
+    sees ``y[M, D_out]``.  Raises :class:`NativeLibraryError` when the block is not eligible
+    (``fuseml_sm100_mlp_small_workspace_bytes`` returns -1); callers then launch the two Linears
+    separately."""
+    lib = N.load()
+    if x.dim() != 2 or w1.dim() != 2 or w2.dim() != 2 or not (x.is_cuda and w1.is_cuda and w2.is_cuda):
+        raise N.NativeLibraryError("fused_mlp expects 2-D CUDA tensors x[M, D_in], w1[I, D_in], w2[D_out, I]")
+    if not (x.dtype == w1.dtype == w2.dtype):
+        raise N.NativeLibraryError("x, w1 and w2 must share one dtype")
+    M, D_in = x.shape
+    I, D_in2 = w1.shape
+    D_out, I2 = w2.shape
+    if D_in != D_in2 or I != I2:
+        raise N.NativeLibraryError(f"shape mismatch: x{tuple(x.shape)} w1{tuple(w1.shape)} w2{tuple(w2.shape)}")
+    for t in (x, w1, w2):
+        if t.stride(1) != 1:
+            raise N.NativeLibraryError("x, w1 and w2 must be row-major (unit stride along their last dimension)")
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty_strided((M, D_out), (D_out, 1), dtype=out_dtype, device=x.device)
+    d = N.MlpDesc()
+    d.M, d.D_in, d.I, d.D_out = M, D_in, I, D_out
+    d.x, d.ldx = x.data_ptr(), x.stride(0)
+    d.w1, d.ldw1 = w1.data_ptr(), w1.stride(0)
+    d.w2, d.ldw2 = w2.data_ptr(), w2.stride(0)
+    d.ab_dtype, d.out_dtype = dtype_code(x.dtype), dtype_code(out_dtype)
+    d.y, d.ldy = out.data_ptr(), out.stride(0)
+    d.flags = N.MLP_WEIGHTS_EXPANDED if weights_expanded else 0
+    slot = 0
+    for prog, ops, cols, which in ((prog1, d.ops1, I, "n_ops1"), (prog2, d.ops2, D_out, "n_ops2")):
+        n = 0
+        if prog is not None:
+            base = slot
+            for t in prog.operands:
+                if slot >= N.MAX_OPERANDS:
+                    raise N.NativeLibraryError(f"the two programs use more than {N.MAX_OPERANDS} external tensors")
+                sm, sn = _broadcast_strides(t, M, cols)
+                o = d.operands[slot]
+                o.ptr, o.stride_m, o.stride_n, o.dtype = t.data_ptr(), sm, sn, dtype_code(t.dtype)
+                slot += 1
+            for i, (opcode, s, imm) in enumerate(prog.ops):
+                ops[i].opcode, ops[i].slot, ops[i].imm = opcode, base + s, imm
+            n = len(prog.ops)
+        setattr(d, which, n)
+    d.n_operands = slot
+    need = lib.fuseml_sm100_mlp_small_workspace_bytes(C.byref(d))
+    if need < 0:
+        raise N.NativeLibraryError("this MLP block cannot run as one kernel (more than 128 rows, an intermediate "
+                                   "width that does not divide into slices, unaligned rows, or a first program "
+                                   "that needs the second value register)")
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(int(need), 16), dtype=torch.uint8, device=x.device)
+    _last_mlp_workspace[0] = workspace
+    d.workspace, d.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    with torch.cuda.device(x.device):
+        rc = lib.fuseml_sm100_mlp_small(C.byref(d), C.c_void_p(stream))
+    N.check(rc, "fuseml_sm100_mlp_small")
+    return out
+
+
 def reduce_tail(x: torch.Tensor, reduce: Iterable[str], axis=None) -> dict[str, torch.Tensor]:
     """Stand-alone sum / max / mean over a 2-D CUDA tensor (fp32 results)."""
     lib = N.load()

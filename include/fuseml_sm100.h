@@ -257,6 +257,41 @@ int fuseml_sm100_gemm_epilogue_noalloc(const fuseml_gemm_desc_t* desc, const fus
                                        void* cuda_stream);
 int64_t fuseml_sm100_noalloc_scratch_bytes(void);
 
+/* ---- both Linears of a small-M MLP block in one kernel ---------------------
+ * y = prog2(prog1(x @ w1^T) @ w2^T) for M <= 128 rows: the intermediate h = prog1(x @ w1^T) is handed
+ * from the first GEMM to the second through shared memory and never reaches global memory.  No
+ * counterpart in the reference, which runs the two Linears as two kernels with h in HBM between them
+ * (benchmarks/bench_mlp_block.py:160-182).  Weights are the nn.Linear tensors as stored:
+ * w1[I, D_in], w2[D_out, I], row-major.  prog1 (ops1) runs on h[M, I], prog2 (ops2) on y[M, D_out];
+ * both index the shared operand table with their own [m, n].  SAVE / SWAP / *_SAVED and STORE_AUX are
+ * not available in ops1.  fp32 runs as 3xTF32.  Work: every CTA takes slices of I, a second pass
+ * folds the CTAs' partial outputs in a fixed order (deterministic) and runs prog2.                 */
+typedef struct {
+  int64_t M, D_in, I, D_out;
+  const void* x;   int64_t ldx;    /* x[M, D_in], D_in contiguous                        */
+  const void* w1;  int64_t ldw1;   /* w1[I, D_in] row-major                              */
+  const void* w2;  int64_t ldw2;   /* w2[D_out, I] row-major                             */
+  int32_t ab_dtype, out_dtype;     /* operands (x, w1, w2 share one dtype) and y         */
+  void* y;         int64_t ldy;
+  int32_t n_ops1, n_ops2, n_operands;
+  int32_t flags;                   /* FUSEML_MLP_WEIGHTS_EXPANDED                        */
+  fuseml_epi_op_t ops1[FUSEML_MAX_EPI_OPS];
+  fuseml_epi_op_t ops2[FUSEML_MAX_EPI_OPS];
+  fuseml_operand_t operands[FUSEML_MAX_OPERANDS];
+  void* workspace;                 /* fuseml_sm100_mlp_small_workspace_bytes(desc) bytes */
+  int64_t workspace_bytes;
+} fuseml_mlp_desc_t;
+
+/* fp32 only: the expansions of w1 and w2 found in the workspace are still valid (same contract
+ * as FUSEML_PLAN_B_EXPANSION_VALID). */
+#define FUSEML_MLP_WEIGHTS_EXPANDED 1
+
+/* Bytes of workspace, or -1 when the block cannot run as one kernel (M > 128, reductions of I that
+ * do not divide into slices, rows that are not multiples of 16 bytes, ...): the caller then launches
+ * the two Linears separately with fuseml_sm100_gemm_epilogue. */
+int64_t fuseml_sm100_mlp_small_workspace_bytes(const fuseml_mlp_desc_t* desc);
+int fuseml_sm100_mlp_small(const fuseml_mlp_desc_t* desc, void* cuda_stream);
+
 /* Stand-alone reduction tail over an existing [M,N] matrix (used when the
  * reduction cannot be absorbed into the producing GEMM): sum / max / mean
  * over rows, columns or everything; fp32 results.  Replaces the eager

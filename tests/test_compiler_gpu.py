@@ -40,7 +40,13 @@ def test_compiled_module_matches_reference_fixture(native_lib, golden_dir, name)
     torch.cuda.synchronize()
     assert F.device_status() == 0
     assert comp.fusion_applied and comp.fusion_strategy == "sm100", comp.declined
-    assert sum(L.launch_count for L in set(comp.launchers)) == 2 * EXPECTED_KERNELS[name]
+    if name == "cfg1":
+        # 128 rows: the two Linears were merged and both calls ran as one kernel each
+        (mlp,) = comp.mlp_launchers
+        assert mlp.fused_count == 2 and sum(L.launch_count for L in set(comp.launchers)) == 0
+    else:
+        assert not comp.mlp_launchers
+        assert sum(L.launch_count for L in set(comp.launchers)) == 2 * EXPECTED_KERNELS[name]
     if not isinstance(out, (tuple, list)):
         out, out2 = (out,), (out2,)
     golden = np.load(golden_dir / f"numeric_{name}.npz")
@@ -350,4 +356,33 @@ def test_training_step_runs_fused_forward_and_backward(native_lib, dtype):
     close(x.grad, x_ref.grad, "dx")
     for (name, p), p_ref in zip(model.named_parameters(), ref_model.parameters()):
         close(p.grad, p_ref.grad, f"d{name}")
+    torch._dynamo.reset()
+
+
+def test_small_batch_mlp_runs_as_one_kernel_and_larger_batches_as_two(native_lib):
+    """Two chained Linears compiled at 64 rows are merged into one launcher that runs both in one
+    kernel (h in shared memory); the same module compiled at 200 rows keeps its two fused launches.
+    Same values either way, against eager."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+
+    torch.manual_seed(11)
+    block = torch.nn.Sequential(torch.nn.Linear(256, 1024), torch.nn.GELU(), torch.nn.Linear(1024, 256)).to("cuda", torch.bfloat16)
+    for rows, merged in ((64, True), (200, False)):
+        torch._dynamo.reset()
+        x = torch.randn(rows, 256, device="cuda", dtype=torch.bfloat16)
+        comp = F.FuseMLCompiler()
+        with torch.no_grad():
+            y = torch.compile(block, backend=comp)(x)
+            ref = block.float()(x.float())
+            block.to(torch.bfloat16)
+        torch.cuda.synchronize()
+        assert F.device_status() == 0
+        assert len(comp.launchers) == 2 and (len(comp.mlp_launchers) == 1) == merged
+        if merged:
+            assert comp.mlp_launchers[0].fused_count == 1
+        else:
+            assert sum(L.launch_count for L in comp.launchers) == 2
+        np.testing.assert_allclose(y.float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
     torch._dynamo.reset()

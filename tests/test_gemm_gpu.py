@@ -660,3 +660,59 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_launch_is_correct(K, clus
     _status_ok(K)
     assert torch.equal(again, good)
     np.testing.assert_allclose(good.float().cpu().numpy(), (a.float() @ w.float().t()).cpu().numpy(), **BF16_TOL)
+
+
+# ---- both Linears of a small-M block in one kernel -------------------------------------------
+
+MLP_CASES = [
+    ("f32", 128, 512, 2048, 512),       # the fp32 parity configuration (cfg1)
+    ("bf16", 128, 512, 2048, 512),
+    ("bf16", 37, 256, 1024, 300),       # ragged rows, an output width that is not a multiple of 256
+    ("f16", 64, 128, 576, 128),         # 576 = 9 slices of 64: more slices than 128-wide candidates allow
+    ("f32", 100, 96, 160, 264),         # 160 = 5 slices of 32
+    ("bf16", 128, 1024, 8192, 1024),    # several slices per CTA (64 slices on 16 CTAs per output chunk)
+]
+
+
+@pytest.mark.parametrize("dtype,M,D,I,Dout", MLP_CASES)
+def test_small_mlp_block_in_one_kernel_matches_two_stage_oracle(K, dtype, M, D, I, Dout):
+    """y = (gelu(x W1^T + b1)) W2^T + b2 + r with h handed over in shared memory, against the oracle
+    run as two fused stages (h rounded to the storage dtype between them, as the kernel does)."""
+    td = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    g = torch.Generator().manual_seed(M + D + I + Dout)
+    x = torch.randn(M, D, generator=g).to(td)
+    w1 = (torch.randn(I, D, generator=g) / D ** 0.5).to(td)
+    b1 = (torch.randn(I, generator=g) * 0.1).to(td)
+    w2 = (torch.randn(Dout, I, generator=g) / I ** 0.5).to(td)
+    b2 = (torch.randn(Dout, generator=g) * 0.1).to(td)
+    r = torch.randn(M, Dout, generator=g).to(td)
+    f = lambda t: t.float().numpy()
+    h = chain.fused_chain(f(x), f(w1).T, [("bias", f(b1)), ("gelu",)], out_dtype=dtype)["d"]
+    ref = chain.fused_chain(h, f(w2).T, [("bias", f(b2)), ("add", f(r))], out_dtype=dtype)["d"]
+    dev = [t.cuda() for t in (x, w1, b1, w2, b2, r)]
+    xd, w1d, b1d, w2d, b2d, rd = dev
+    outs = []
+    for _ in range(2):                         # twice: the second call finds the barriers' memory used
+        y = K.fused_mlp(xd, w1d, w2d, K.EpilogueProgram().bias(b1d).gelu(), K.EpilogueProgram().bias(b2d).add_tensor(rd))
+        torch.cuda.synchronize()
+        _status_ok(K)
+        outs.append(y)
+    assert torch.equal(outs[0], outs[1]), "deterministic"
+    tol = {"bf16": BF16_TOL, "f16": dict(rtol=4e-3, atol=4e-3), "f32": F32_TOL}[dtype]
+    np.testing.assert_allclose(outs[0].float().cpu().numpy(), ref, **tol)
+    # and the same block as two separate fused launches
+    h2 = K.fused_gemm(xd, w1d.t(), K.EpilogueProgram().bias(b1d).gelu())
+    y2 = K.fused_gemm(h2, w2d.t(), K.EpilogueProgram().bias(b2d).add_tensor(rd))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(outs[0].float().cpu().numpy(), y2.float().cpu().numpy(), **tol)
+
+
+def test_small_mlp_block_declines_what_it_cannot_run(K):
+    x = torch.zeros(200, 64, dtype=torch.bfloat16, device="cuda")      # more than 128 rows
+    w1 = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    w2 = torch.zeros(64, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="one kernel"):
+        K.fused_mlp(x, w1, w2)
+    with pytest.raises(RuntimeError, match="one kernel"):               # 100 columns of I: no slice width divides it
+        K.fused_mlp(x[:64], torch.zeros(104, 64, dtype=torch.bfloat16, device="cuda"),
+                    torch.zeros(64, 104, dtype=torch.bfloat16, device="cuda"))
