@@ -339,8 +339,8 @@ class GemmRowReduce(Workload):
 
 class SmallFp32MLP(Workload):
     """cfg1: fp32 ``linear2(gelu(linear1(x)))`` at M = 128 (a latency-bound parity configuration:
-    both Linears run in ONE kernel on 3xTF32 operands, bias + GELU between them with h handed over
-    in shared memory, the second bias in the pass that folds the CTAs' partial outputs)."""
+    both Linears run the fused kernel on 3xTF32 operands, the first with bias + GELU, the second
+    with its bias alone as the epilogue; no library GEMM is left in the step)."""
 
     name = "cfg1_fp32_mlp_small"
     dtype = "f32"
@@ -371,10 +371,9 @@ class SmallFp32MLP(Workload):
         self.algo_bytes = 4.0 * (rows * d_model + 2 * d_model * d_inter + d_inter + d_model + rows * d_model) \
             + 8.0 * rows * d_inter
         self.expected_kernels = 2
-        # the two launchers are merged (128 rows): one expansion launch for x, W1 and W2, the kernel
-        # that runs both Linears with h in shared memory, and the pass that folds its partial outputs
-        self.launches_per_step = 3
-        self.gemm_launches_per_step = 1
+        # per Linear: the operand expansion, the split-K GEMM and its finish pass
+        self.launches_per_step = 6
+        self.gemm_launches_per_step = 2
         self.h2d_bytes = rows * d_model * 4
         self.d2h_bytes = rows * d_model * 4
 

@@ -175,6 +175,23 @@ static int launch_bn(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 #undef FUSEML_DISPATCH
 }
 
+// The pass that folds split-K (or small-MLP) partial tiles and runs the epilogue program.  Few
+// tiles: eight columns per thread instead of sixteen, so that twice as many threads share the
+// latency of reading the slices.
+static int launch_finish(const GemmParams& pf, int64_t num_tiles, int bn, cudaStream_t stream) {
+  const int64_t items16 = num_tiles * kTileM * (bn / 16);
+  if (items16 < 148 * 256 * 2) {
+    const int blocks = static_cast<int>((2 * items16 + 255) / 256);
+    if (pf.uses_saved) splitk_finish_kernel<true, 8><<<blocks, 256, 0, stream>>>(pf);
+    else splitk_finish_kernel<false, 8><<<blocks, 256, 0, stream>>>(pf);
+  } else {
+    const int blocks = static_cast<int>((items16 + 255) / 256);
+    if (pf.uses_saved) splitk_finish_kernel<true, 16><<<blocks, 256, 0, stream>>>(pf);
+    else splitk_finish_kernel<false, 16><<<blocks, 256, 0, stream>>>(pf);
+  }
+  return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+}
+
 // Peephole over the epilogue program: the diamond gelu_erf(h) * sigmoid(h), written with the
 // second value register as SAVE, GELU_ERF, SWAP, SIGMOID, MUL_SAVED (or with the two branches
 // the other way round), becomes the single op FUSEML_OP_GELU_ERF_MUL_SIGMOID, which shares one
@@ -459,13 +476,9 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
       pf.kb_per_split = per;
       pf.split_ws = pg.split_ws;
       for (int i = 0; i < pf.n_ops; ++i) pf.ops[i].reserved = 0;   // operands come straight from global memory
-      const int64_t work = static_cast<int64_t>(p.num_tiles) * kTileM * (BN / kFinishChunk);
-      const int blocks = static_cast<int>((work + 255) / 256);
       // an ordinary launch: as a programmatic dependent (scheduled early, waiting on the device)
       // it measured 20-35 % slower at high slice counts
-      if (pf.uses_saved) splitk_finish_kernel<true><<<blocks, 256, 0, stream>>>(pf);
-      else splitk_finish_kernel<false><<<blocks, 256, 0, stream>>>(pf);
-      return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+      return launch_finish(pf, p.num_tiles, BN, stream);
     }
   }
 
@@ -639,7 +652,7 @@ int fuseml_sm100_mlp_small(const fuseml_mlp_desc_t* desc, void* cuda_stream) {
   CUtensorMap tx, t1, t2;
   if ((rc = encode_2d(&tx, desc->ab_dtype, x, desc->M, K1, ldx, BK, 128)) != FUSEML_OK) return rc;
   if ((rc = encode_2d(&t1, desc->ab_dtype, w1, desc->I, K1, ldw1, BK, L.bi)) != FUSEML_OK) return rc;
-  if ((rc = encode_2d(&t2, desc->ab_dtype, w2, desc->D_out, K2, ldw2, BK, 256)) != FUSEML_OK) return rc;
+  if ((rc = encode_2d(&t2, desc->ab_dtype, w2, desc->D_out, K2, ldw2, BK, 128)) != FUSEML_OK) return rc;
 
   void* status_ptr = nullptr;
   if (cudaGetSymbolAddress(&status_ptr, g_status_word) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_DEVICE; }
@@ -696,6 +709,7 @@ int fuseml_sm100_mlp_small(const fuseml_mlp_desc_t* desc, void* cuda_stream) {
   p2.split_k = L.groups;
   p2.split_ws = q.split_ws;
 
+  const int smem_bytes = f32 ? mlp::Layout<true>::kDynamicBytes : mlp::Layout<false>::kDynamicBytes;
   {
     static std::mutex mutex;
     static bool configured[kMaxDevices] = {false};
@@ -703,7 +717,10 @@ int fuseml_sm100_mlp_small(const fuseml_mlp_desc_t* desc, void* cuda_stream) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return FUSEML_E_DEVICE; }
     std::lock_guard<std::mutex> lock(mutex);
     if (!configured[dev]) {
-      if (cudaFuncSetAttribute(mlp::mlp_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mlp::kDynamicBytes) != cudaSuccess) {
+      if (cudaFuncSetAttribute(mlp::mlp_small_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               mlp::Layout<true>::kDynamicBytes) != cudaSuccess ||
+          cudaFuncSetAttribute(mlp::mlp_small_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               mlp::Layout<false>::kDynamicBytes) != cudaSuccess) {
         cudaGetLastError();
         return FUSEML_E_LAUNCH;
       }
@@ -717,15 +734,13 @@ int fuseml_sm100_mlp_small(const fuseml_mlp_desc_t* desc, void* cuda_stream) {
   cfg.attrs = attr; cfg.numAttrs = 1;
   cfg.gridDim = dim3(L.groups * L.n_dchunks);
   cfg.blockDim = dim3(mlp::kThreads);
-  cfg.dynamicSmemBytes = mlp::kDynamicBytes;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
-  if (cudaLaunchKernelEx(&cfg, mlp::mlp_small_kernel, tx, t1, t2, q, p1) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_LAUNCH; }
+  const cudaError_t le = f32 ? cudaLaunchKernelEx(&cfg, mlp::mlp_small_kernel<true>, tx, t1, t2, q, p1)
+                             : cudaLaunchKernelEx(&cfg, mlp::mlp_small_kernel<false>, tx, t1, t2, q, p1);
+  if (le != cudaSuccess) { cudaGetLastError(); return FUSEML_E_LAUNCH; }
 
-  const int64_t work = static_cast<int64_t>(L.n_dchunks) * kTileM * (256 / kFinishChunk);
-  const int blocks = static_cast<int>((work + 255) / 256);
-  if (p2.uses_saved) splitk_finish_kernel<true><<<blocks, 256, 0, stream>>>(p2);
-  else splitk_finish_kernel<false><<<blocks, 256, 0, stream>>>(p2);
-  return cudaGetLastError() == cudaSuccess ? FUSEML_OK : FUSEML_E_LAUNCH;
+  return launch_finish(p2, L.n_dchunks, 256, stream);
 }
 
 int fuseml_sm100_reduce_tail(const void* x, int32_t dtype, int64_t M, int64_t N, int64_t ldx,

@@ -10,8 +10,8 @@
 // program (bias, residual, ...).  Deterministic; no atomics.
 //
 //   warp 0  one thread: TMA producer.  One ring, two kinds of jobs in program order per slice:
-//           K blocks of the first GEMM (x tile 128 x 128 B + W1 rows of the slice) and K blocks
-//           of the second (W2 tile 256 x 128 B; its A operand is h in shared memory)
+//           K blocks of the first GEMM (x tile 128 x 128 B + W1 rows of the slice) and half K
+//           blocks of the second (128 rows of W2 x 128 B; its A operand is h in shared memory)
 //   warp 1  one thread: tcgen05.mma issuer for both GEMMs; allocates TMEM
 //   warps 2-5  first epilogue (one TMEM lane quarter each) and the final partial store
 //
@@ -36,18 +36,26 @@
 namespace fuseml {
 namespace mlp {
 
-constexpr int kStages = 3;
-constexpr int kABytes = 128 * 128;            // x tile: 128 rows x 128 bytes of K
-constexpr int kBBytes = 256 * 128;            // W tile: up to 256 rows x 128 bytes of K
-constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kABytes = 128 * 128;            // x tile / h tile / half a W2 tile: 128 rows x 128 bytes of K
 constexpr int kHTiles = 4;                     // h tiles of 128 rows x 128 bytes
-constexpr int kHOffset = kStages * kStageBytes;
-constexpr int kBarOffset = kHOffset + kHTiles * kABytes;
-constexpr int kNumBars = 2 * kStages + 3;      // ring full / empty, acc1 full, h full, acc2 full
-constexpr int kDynamicBytes = kBarOffset + kNumBars * 8 + 16 + 1024;
 constexpr int kThreads = 192;
 constexpr uint32_t kAcc2Col = 0;               // second accumulator: TMEM columns [0, 256)
 constexpr uint32_t kAcc1Col = 256;             // first accumulator: TMEM columns [256, 256 + bi)
+
+// Shared memory per operand format.  A ring stage holds one K block of the first GEMM (the x tile,
+// 16 KB, and the slice's rows of W1: at most 64 rows for tf32, 128 for 16-bit operands) or one
+// half K block of the second (128 rows of W2, 16 KB, at the stage base).  The first GEMM's K loop is
+// a chain of load latencies (48 K blocks for the fp32 configuration), so the ring is as deep as
+// shared memory allows: six stages of 24 KB for tf32, four of 32 KB for 16-bit operands.
+template <bool TF32>
+struct Layout {
+  static constexpr int kStages = TF32 ? 6 : 4;
+  static constexpr int kStageBytes = kABytes + (TF32 ? 64 : 128) * 128;
+  static constexpr int kHOffset = kStages * kStageBytes;
+  static constexpr int kBarOffset = kHOffset + kHTiles * kABytes;
+  static constexpr int kNumBars = 2 * kStages + 3;      // ring full / empty, acc1 full, h full, acc2 full
+  static constexpr int kDynamicBytes = kBarOffset + kNumBars * 8 + 16 + 1024;
+};
 
 enum : int32_t {
   kWhereMlpProducer = 0x301,
@@ -72,10 +80,17 @@ struct MlpParams {
 };
 
 // prog1 is a GemmParams of which only the program (n_ops, ops, operands) and N (= I) are used.
+template <bool TF32>
 __global__ void __launch_bounds__(kThreads, 1)
 mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w1,
                  const __grid_constant__ CUtensorMap tmap_w2, const __grid_constant__ MlpParams q,
                  const __grid_constant__ GemmParams prog1) {
+  using L = Layout<TF32>;
+  constexpr int kStages = L::kStages;
+  constexpr int kStageBytes = L::kStageBytes;
+  constexpr int kHOffset = L::kHOffset;
+  constexpr int kBarOffset = L::kBarOffset;
+  constexpr int kNumBars = L::kNumBars;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
@@ -89,10 +104,10 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool tf32 = q.fmt == 2;
-  const int32_t bk = tf32 ? 32 : 64;                 // elements per 128-byte row
+  constexpr bool tf32 = TF32;
+  constexpr int32_t bk = tf32 ? 32 : 64;             // elements per 128-byte row
   const int32_t sub = q.bi / bk;                     // 128-byte column blocks of h per slice
-  const int32_t n2 = sub * (tf32 ? 3 : 1);           // K blocks of the second GEMM per slice
+  const int32_t n2 = sub * (tf32 ? 3 : 1) * 2;       // jobs of the second GEMM per slice: K blocks x two 128-row halves of W2
   const int32_t group = static_cast<int32_t>(blockIdx.x) % q.groups;
   const int32_t dchunk = static_cast<int32_t>(blockIdx.x) / q.groups;
   const int32_t d0 = dchunk * 256;
@@ -139,11 +154,12 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
             ptx::tma_load_2d(a_dst, &tmap_x, full_bar(stage), job * bk, 0);
             ptx::tma_load_2d(b_dst, &tmap_w1, full_bar(stage), job * bk, s * q.bi);
           } else {
-            // second GEMM: 256 rows of W2, the slice's columns (for tf32: copy j of the expansion)
-            const int32_t r = job - q.kb1;
+            // second GEMM: 128 rows of W2 (half of the output chunk), the slice's columns (for
+            // tf32: copy j of the expansion), at the stage base
+            const int32_t r = (job - q.kb1) >> 1, half = (job - q.kb1) & 1;
             const int32_t t = tf32 ? r / 3 : r, j = tf32 ? r % 3 : 0;
-            ptx::mbar_arrive_expect_tx(full_bar(stage), kBBytes);
-            ptx::tma_load_2d(b_dst, &tmap_w2, full_bar(stage), j * q.I + s * q.bi + t * bk, d0);
+            ptx::mbar_arrive_expect_tx(full_bar(stage), kABytes);
+            ptx::tma_load_2d(a_dst, &tmap_w2, full_bar(stage), j * q.I + s * q.bi + t * bk, d0 + half * 128);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -155,18 +171,19 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (ptx::elect_one()) {
       const uint32_t fmt = static_cast<uint32_t>(q.fmt);
       const uint32_t idesc1 = ptx::make_idesc(fmt, 0u, 0u, 128, static_cast<uint32_t>(q.bi));
-      const uint32_t idesc2 = ptx::make_idesc(fmt, 0u, 0u, 128, 256u);
+      const uint32_t idesc2 = ptx::make_idesc(fmt, 0u, 0u, 128, 128u);
       const uint64_t a_desc0 = ptx::make_smem_desc_sw128(smem_base, 16u, 1024u);
       const uint64_t b_desc0 = ptx::make_smem_desc_sw128(smem_base + kABytes, 16u, 1024u);
       const uint64_t h_desc0 = ptx::make_smem_desc_sw128(smem_base + kHOffset, 16u, 1024u);
       int stage = 0;
       uint32_t phase = 0, h_phase = 0;
-      bool ok = true, first2 = true, any = false;
+      bool ok = true, any = false;
+      bool first2[2] = {true, true};
       auto issue4 = [&](uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool fresh) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint32_t accumulate = (!fresh || k > 0) ? 1u : 0u;
-          if (tf32) ptx::mma_tf32_ss(d_tmem, a_desc + k * 2, b_desc + k * 2, idesc, accumulate);
+          if constexpr (tf32) ptx::mma_tf32_ss(d_tmem, a_desc + k * 2, b_desc + k * 2, idesc, accumulate);
           else ptx::mma_f16_ss(d_tmem, a_desc + k * 2, b_desc + k * 2, idesc, accumulate);
         }
       };
@@ -186,15 +203,17 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         if (!ptx::mbar_wait(h_full, h_phase, abort_flag, q.status, kWhereMlpMmaH)) { ok = false; break; }
         h_phase ^= 1u;
         ptx::tc_fence_after_sync();
-        for (int32_t r = 0; r < n2; ++r) {
+        for (int32_t job = 0; job < n2; ++job) {
           if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag, q.status, kWhereMlpMmaFull)) { ok = false; break; }
           ptx::tc_fence_after_sync();
           // tf32: K block r = 3 t + j multiplies [hi | lo | hi][j] of h column block t with copy j of W2
+          const int32_t r = job >> 1, half = job & 1;
           const int32_t t = tf32 ? r / 3 : r, j = tf32 ? r % 3 : 0;
           const int32_t tile = tf32 ? (2 * t + (j == 1 ? 1 : 0)) : t;
           const uint64_t off = static_cast<uint64_t>(stage) * (kStageBytes >> 4);
-          issue4(tmem_base + kAcc2Col, h_desc0 + static_cast<uint64_t>(tile) * (kABytes >> 4), b_desc0 + off, idesc2, first2);
-          first2 = false;
+          issue4(tmem_base + kAcc2Col + static_cast<uint32_t>(half * 128), h_desc0 + static_cast<uint64_t>(tile) * (kABytes >> 4),
+                 a_desc0 + off, idesc2, first2[half]);
+          first2[half] = false;
           ptx::mma_commit(empty_bar(stage));
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }

@@ -12,15 +12,16 @@
 
 namespace fuseml {
 
-constexpr int kFinishChunk = 16;
+constexpr int kFinishChunk = 16;      // columns per thread; 8 for small problems (twice the threads)
 
 // Partial tiles are stored as [slice][tile][16-byte piece = column / 4][row][4 floats] (see the
 // GEMM kernel): a thread takes one row and four consecutive pieces (16 columns); threads that
 // are neighbours in a warp take neighbouring rows, so every load instruction of a warp reads
 // 512 contiguous bytes.
-template <bool USES_SAVED>
+template <bool USES_SAVED, int CHUNK = kFinishChunk>
 __global__ void __launch_bounds__(256) splitk_finish_kernel(const __grid_constant__ GemmParams p) {
-  const int32_t groups_per_tile = p.bn / kFinishChunk;               // 16-column groups in a tile
+  constexpr int kFinishChunk = CHUNK;                                 // shadows the default: columns per thread
+  const int32_t groups_per_tile = p.bn / kFinishChunk;               // column groups in a tile
   const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   const int32_t row = static_cast<int32_t>(idx % kTileM);
   const int64_t rest = idx / kTileM;
