@@ -360,9 +360,9 @@ def fused_mlp(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, prog1: Epilog
     d.n_operands = slot
     need = lib.fuseml_sm100_mlp_small_workspace_bytes(C.byref(d))
     if need < 0:
-        raise N.NativeLibraryError("this MLP block cannot run as one kernel (more than 128 rows, an intermediate "
-                                   "width that does not divide into slices, unaligned rows, or a first program "
-                                   "that needs the second value register)")
+        raise N.NativeLibraryError("this MLP block cannot run as one kernel (more than 128 rows, an output wider than "
+                                   "512 columns, an intermediate width that does not divide into slices, unaligned "
+                                   "rows, or a first program that needs the second value register)")
     if workspace is None or workspace.numel() * workspace.element_size() < need:
         workspace = torch.empty(max(int(need), 16), dtype=torch.uint8, device=x.device)
     _last_mlp_workspace[0] = workspace

@@ -286,9 +286,10 @@ typedef struct {
  * as FUSEML_PLAN_B_EXPANSION_VALID). */
 #define FUSEML_MLP_WEIGHTS_EXPANDED 1
 
-/* Bytes of workspace, or -1 when the block cannot run as one kernel (M > 128, reductions of I that
- * do not divide into slices, rows that are not multiples of 16 bytes, ...): the caller then launches
- * the two Linears separately with fuseml_sm100_gemm_epilogue. */
+/* Bytes of workspace, or -1 when the block cannot run as one kernel (M > 128, D_out > 512, an I that
+ * does not divide into slices of 128 / 64 (16-bit) or 64 / 32 (fp32) columns, rows that are not
+ * multiples of 16 bytes, ...): the caller then launches the two Linears separately with
+ * fuseml_sm100_gemm_epilogue. */
 int64_t fuseml_sm100_mlp_small_workspace_bytes(const fuseml_mlp_desc_t* desc);
 int fuseml_sm100_mlp_small(const fuseml_mlp_desc_t* desc, void* cuda_stream);
 

@@ -670,7 +670,7 @@ MLP_CASES = [
     ("bf16", 37, 256, 1024, 300),       # ragged rows, an output width that is not a multiple of 256
     ("f16", 64, 128, 576, 128),         # 576 = 9 slices of 64: more slices than 128-wide candidates allow
     ("f32", 100, 96, 160, 264),         # 160 = 5 slices of 32
-    ("bf16", 128, 1024, 8192, 1024),    # several slices per CTA (64 slices on 16 CTAs per output chunk)
+    ("bf16", 128, 1024, 8192, 512),     # several slices per CTA (64 slices on 32 CTAs per output chunk)
 ]
 
 
@@ -713,6 +713,9 @@ def test_small_mlp_block_declines_what_it_cannot_run(K):
     w2 = torch.zeros(64, 128, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="one kernel"):
         K.fused_mlp(x, w1, w2)
-    with pytest.raises(RuntimeError, match="one kernel"):               # 100 columns of I: no slice width divides it
+    with pytest.raises(RuntimeError, match="one kernel"):               # an output wider than two 256-column chunks
+        K.fused_mlp(x[:64], torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda"),
+                    torch.zeros(1024, 128, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(RuntimeError, match="one kernel"):               # 104 columns of I: no slice width divides it
         K.fused_mlp(x[:64], torch.zeros(104, 64, dtype=torch.bfloat16, device="cuda"),
                     torch.zeros(64, 104, dtype=torch.bfloat16, device="cuda"))
