@@ -13,7 +13,8 @@
 //           K blocks of the first GEMM (x tile 128 x 128 B + W1 rows of the slice) and half K
 //           blocks of the second (128 rows of W2 x 128 B; its A operand is h in shared memory)
 //   warp 1  one thread: tcgen05.mma issuer for both GEMMs; allocates TMEM
-//   warps 2-5  first epilogue (one TMEM lane quarter each) and the final partial store
+//   warps 2-9  first epilogue (two warps per TMEM lane quarter, alternating 32-column chunks)
+//           and the final partial store
 //
 // fp32 runs as 3xTF32 like the stand-alone kernel: x, W1 and W2 arrive expanded ([hi|lo|hi] and
 // [hi|hi|lo] along K); h is split into hi (top 10 mantissa bits) and lo = h - hi on the fly, two
@@ -38,7 +39,8 @@ namespace mlp {
 
 constexpr int kABytes = 128 * 128;            // x tile / h tile / half a W2 tile: 128 rows x 128 bytes of K
 constexpr int kHTiles = 4;                     // h tiles of 128 rows x 128 bytes
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;                  // two per TMEM lane quarter, alternating 32-column chunks
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr uint32_t kAcc2Col = 0;               // second accumulator: TMEM columns [0, 256)
 constexpr uint32_t kAcc1Col = 256;             // first accumulator: TMEM columns [256, 256 + bi)
 
@@ -115,7 +117,7 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
     ptx::mbar_init(acc1_full, 1);
-    ptx::mbar_init(h_full, 4);          // one arrival per epilogue warp
+    ptx::mbar_init(h_full, kEpiWarps);  // one arrival per epilogue warp
     ptx::mbar_init(acc2_full, 1);
     abort_flag[0] = 0u;
     abort_flag[1] = q.wait_limit_us;
@@ -224,6 +226,7 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
   } else {
     // ------------------------------ epilogue warps -------------------------------------------
     const int quarter = warp & 3;                         // TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2;                     // which of the quarter's two warps
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const bool row_ok = row < q.M;
@@ -236,7 +239,7 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
       acc1_phase ^= 1u;
       if (!ok) continue;
       ptx::tc_fence_after_sync();
-      for (int32_t c = 0; c < q.bi / 32; ++c) {
+      for (int32_t c = half; c < q.bi / 32; c += 2) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + lane_base + kAcc1Col + static_cast<uint32_t>(c * 32), r);
         ptx::tmem_ld_wait();
@@ -294,7 +297,7 @@ mlp_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (any && ok && ptx::mbar_wait(acc2_full, 0u, abort_flag, q.status, kWhereMlpEpiAcc2, true)) {
       ptx::tc_fence_after_sync();
       float4* tile = reinterpret_cast<float4*>(q.split_ws + (static_cast<int64_t>(group) * q.n_dchunks + dchunk) * (128 * 256));
-      for (int32_t c = 0; c < 256 / 32; ++c) {
+      for (int32_t c = half; c < 256 / 32; c += 2) {
         if (d0 + c * 32 >= q.D_out) break;
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + lane_base + kAcc2Col + static_cast<uint32_t>(c * 32), r);
