@@ -105,7 +105,7 @@ class FuseMLCompiler:
         # `fuse_mlp=True`: pairs of chained launchers are merged into one call that runs both Linears
         # in one kernel when the batch has at most 128 rows (FusedMLPLauncher).  Off by default: at
         # the sizes measured (128 x 512 x 2048 x 512) the one kernel, a serial chain of two K loops
-        # and two epilogues per CTA, is 7 % (fp32) to 20 % (bf16) slower than the two split-K launches
+        # and two epilogues per CTA, is on a par with the two split-K launches at best (1-5 % slower)
         self.mlp_launchers: list = []
         self.fuse_mlp = bool(fuse_mlp)
         self.declined: list[tuple[str, str]] = []
