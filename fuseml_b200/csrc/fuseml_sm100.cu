@@ -231,7 +231,9 @@ static int check_plan(const fuseml_plan_t* pl) {
   if (pl->grid <= 0 || pl->group_m <= 0) return FUSEML_E_PLAN;
   if (pl->cluster != 1 && pl->cluster != 2) return FUSEML_E_PLAN;
   if (pl->cluster == 2 && pl->tile_n <= 128) return FUSEML_E_PLAN;
-  if (pl->split_k < 0 || pl->split_k > 64 || (pl->flags & ~FUSEML_PLAN_B_EXPANSION_VALID) != 0) return FUSEML_E_PLAN;
+  if (pl->split_k < 0 || pl->split_k > 64 || (pl->flags & ~(FUSEML_PLAN_B_EXPANSION_VALID | FUSEML_PLAN_STREAM_K)) != 0)
+    return FUSEML_E_PLAN;
+  if ((pl->flags & FUSEML_PLAN_STREAM_K) && (pl->cluster != 2 || pl->split_k > 1)) return FUSEML_E_PLAN;
   if (pl->split_k > 1 && pl->cluster != 1) return FUSEML_E_PLAN;
   return FUSEML_OK;
 }
@@ -482,7 +484,14 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     }
   }
 
-  int grid = std::min(plan.grid, p.num_tiles * CGr);
+  const bool stream_k = (plan.flags & FUSEML_PLAN_STREAM_K) != 0;
+  int grid = stream_k ? plan.grid : std::min(plan.grid, p.num_tiles * CGr);
+  if (stream_k) {
+    p.stream_k = 1;
+    p.sk_ws = reinterpret_cast<float*>(ws + w.sk_ws_off);
+    p.sk_flags = reinterpret_cast<uint32_t*>(ws + w.sk_flags_off);
+    if (cudaMemsetAsync(p.sk_flags, 0, static_cast<size_t>(w.sk_flags_bytes), stream) != cudaSuccess) { cudaGetLastError(); return FUSEML_E_LAUNCH; }
+  }
   if (desc->reduce.kinds != 0 && desc->reduce.axis == FUSEML_AXIS_ALL) {
     // AXIS_ALL partials: one per launched CTA.  Slots of CTAs that end up not launched (the
     // device holds fewer CTA pairs than asked for) are filled with neutral values first.
@@ -493,7 +502,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   // with sixteen epilogue warps on 16-column chunks (twice the warps in flight for the operand
   // loads, the special-function unit and the stores).  Reductions keep the 8-warp instance
   // (their partial layout is sized for two warps per row).
-  const bool lone_tile = p.num_tiles * CGr <= grid && p.red_kinds == 0 && fmt != 2;
+  const bool lone_tile = p.num_tiles * CGr <= grid && p.red_kinds == 0 && fmt != 2 && !stream_k;
   CUtensorMap tr, td;
   std::memset(&tr, 0, sizeof(tr));
   std::memset(&td, 0, sizeof(td));

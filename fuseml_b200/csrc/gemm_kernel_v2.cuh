@@ -40,6 +40,7 @@ enum : int32_t {
   kWhereProducerDrain = 0x205,
   kWhereEpilogueTileIn = 0x206,
   kWhereStoreBox = 0x207,
+  kWhereStreamKPart = 0x208,
 };
 
 // Optional stall counters (diagnostic builds only, -DFUSEML_STALL_COUNTERS): per CTA
@@ -235,15 +236,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
   if (threadIdx.x == 32) g_stall[blockIdx.x][8] = ptx::globaltimer_ns();
 #endif
-  const int32_t num_kb = p.num_kb;
-  // Split-K launches give every CTA exactly one work item (tile, K slice); otherwise a tile
-  // walker strides over the tiles and owns their whole K loop.
+  // Every role walks the same list of work items (WorkWalk): whole tiles in waves, then (stream-K
+  // launches) a range of the K blocks of the last, ragged wave's tiles; or the single
+  // (tile, K slice) item of a split-K launch.
   const bool splitk = p.split_k > 1;
   const int32_t k_slice = splitk ? unit / p.num_tiles : 0;
-  const int32_t first_tile = splitk ? unit % p.num_tiles : unit;
-  const int32_t tile_step = splitk ? p.num_tiles : num_units;
-  const int32_t kb_begin = splitk ? k_slice * p.kb_per_split : 0;
-  const int32_t kb_end = splitk ? (kb_begin + p.kb_per_split < num_kb ? kb_begin + p.kb_per_split : num_kb) : num_kb;
   // The tile width is a run-time value (a multiple of 32, at most BN): the router may shave it
   // so that the number of tiles fits the number of CTA pairs without a ragged last wave.
   const int32_t bn = p.bn;
@@ -261,9 +258,13 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const uint64_t pol_keep = ptx::policy_evict_last();
       const uint64_t pol_normal = ptx::policy_evict_normal();
       long long st_empty = 0;
-      for (int32_t t = first_tile; t < p.num_tiles && ok; t += tile_step) {
+      WorkWalk walk;
+      walk.init(p, unit, num_units);
+      WorkItem w;
+      while (ok && walk.next(&w)) {
+        const int32_t kb_begin = w.kb0, kb_end = w.kb1;
         int32_t tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
+        tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
         const int32_t m0 = tm * (kTileM * CG) + static_cast<int32_t>(cta_rank) * kTileM;
         const int32_t n0 = tn * bn + static_cast<int32_t>(cta_rank) * bn_cta;
         for (int32_t kb = kb_begin; kb < kb_end; ++kb) {
@@ -275,7 +276,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           FUSEML_STALL_ADD(st_empty);
           // host-injected failure (diagnostics): the last K block of the last tile is never
           // loaded and its barrier never armed; nothing is in flight when the MMA thread gives up
-          if (p.drop_last_load && kb == kb_end - 1 && t + tile_step >= p.num_tiles) break;
+          if (p.drop_last_load && kb == kb_end - 1 && w.last) break;
           const uint32_t a_dst = smem_base + stage * L::kStageBytes;
           const uint32_t b_dst = a_dst + L::kABytes;
           // one load helper for both modes: completion bytes go to `bar` (for a pair: the
@@ -420,7 +421,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
       const long long st_begin = clock64();
 #endif
-      for (int32_t t = first_tile; t < p.num_tiles && ok; t += tile_step) {
+      WorkWalk walk;
+      walk.init(p, unit, num_units);
+      WorkItem w;
+      while (ok && walk.next(&w)) {
+        const int32_t kb_begin = w.kb0, kb_end = w.kb1;
         {
           FUSEML_STALL_T0();
           if (!ptx::mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, kWhereMmaTmemEmpty)) {
@@ -509,7 +514,15 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     // warp-level store writes 32 consecutive 16-byte pieces (512 contiguous bytes) instead of
     // 32 pieces in 32 different rows, and splitk_finish_kernel reads them back the same way.
     float* const split_tile = splitk ? p.split_ws + static_cast<int64_t>(k_slice) * p.num_tiles * (kTileM * bn) : nullptr;
-    for (int32_t t = first_tile; t < p.num_tiles; t += tile_step) {
+    // Stream-K: this CTA's slot for the raw accumulator of a later part, and its flag
+    float* const sk_mine = p.stream_k ? p.sk_ws + (static_cast<int64_t>(unit) * CG + cta_rank) * (kTileM * BN) : nullptr;
+    WorkWalk walk;
+    walk.init(p, unit, num_units);
+    WorkItem w;
+    while (walk.next(&w)) {
+      const int32_t t = w.tile;
+      const bool sk_later = w.kind == 2;       // raw store, no program, no reductions
+      const bool sk_first = w.kind == 1;       // add the later parts, then the usual epilogue
       int32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
       const int32_t tm128 = tm * CG + static_cast<int32_t>(cta_rank);   // index of this CTA's 128-row block
@@ -553,6 +566,24 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           !ptx::mbar_wait(tile_in_bar, 0u, abort_flag, p.status, kWhereEpilogueTileIn, true)) {
         ok = false;
       }
+      if (sk_first && ok) {
+        // the later parts of this tile were stored by the next `after` units, normally long ago
+        // (a unit works on its later part first); bounded wait on their flags all the same
+        for (int32_t j = 1; j <= w.after && ok; ++j) {
+          const volatile uint32_t* flag = p.sk_flags + (static_cast<int64_t>(unit + j) * CG + cta_rank);
+          const uint64_t t0 = ptx::globaltimer_ns();
+          while (*flag == 0u) {
+            __nanosleep(64);
+            const uint32_t limit_us = abort_flag[1];
+            if (*abort_flag || ptx::globaltimer_ns() - t0 > (limit_us ? static_cast<uint64_t>(limit_us) * 1000ull : ptx::kWaitLimitNs)) {
+              if (!*abort_flag) { *abort_flag = 1u; if (p.status) atomicCAS(p.status, 0, kWhereStreamKPart); }
+              ok = false;
+              break;
+            }
+          }
+        }
+        __threadfence();
+      }
 #pragma unroll 1
       for (int c = half; (ok || staged_io) && c < bn / CH; c += kEpiSplit) {
         const int32_t n0 = n_tile0 + c * CH;
@@ -586,11 +617,31 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
           const long long c1 = clock64();
 #endif
-          epi::run_program<PROG, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
+          if (sk_first) {
+            // later parts in unit order: the sum does not depend on which unit finished first
+            for (int32_t j = 1; j <= w.after; ++j) {
+              const float4* src = reinterpret_cast<const float4*>(p.sk_ws + (static_cast<int64_t>(unit + j) * CG + cta_rank) * (kTileM * BN)) +
+                                  static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
+#pragma unroll
+              for (int i = 0; i < CH / 4; ++i) {
+                const float4 x = __ldcg(src + i * kTileM);
+                v[4 * i + 0] += x.x;
+                v[4 * i + 1] += x.y;
+                v[4 * i + 2] += x.z;
+                v[4 * i + 3] += x.w;
+              }
+            }
+          }
+          if (!sk_later) epi::run_program<PROG, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
 #ifdef FUSEML_STALL_COUNTERS
           const long long c2 = clock64();
 #endif
-          if (tile_out) {
+          if (sk_later) {
+            float4* dst = reinterpret_cast<float4*>(sk_mine) + static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
+#pragma unroll
+            for (int i = 0; i < CH / 4; ++i)
+              dst[i * kTileM] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else if (tile_out) {
             if constexpr (CH == 16) epi::store_tile_smem(v, piece, p.out_dtype);
           } else if (splitk) {
             float4* dst = reinterpret_cast<float4*>(split_tile + static_cast<int64_t>(t) * (kTileM * bn)) +
@@ -606,7 +657,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           st_prog += c2 - c1;
           st_store += clock64() - c2;
 #endif
-          if (red_any) {
+          if (red_any && !sk_later) {
             if (p.red_axis == FUSEML_AXIS_M) {
               // column reductions transpose 32 x 32 blocks in registers: 32-column chunks only (the
               // host never picks the 16-warp instance for them)
@@ -654,6 +705,15 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           if (lane == 0) ptx::mbar_arrive(box_bar(c >> 2));
         }
       }
+      if (sk_later) {
+        // publish this part: every thread's stores, then one flag per CTA
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+        if (threadIdx.x == 64 && ok) {
+          *reinterpret_cast<volatile uint32_t*>(p.sk_flags + (static_cast<int64_t>(unit) * CG + cta_rank)) = 1u;
+          __threadfence();
+        }
+      }
       // accumulator drained: hand the TMEM buffer back to the (leader's) MMA thread
       ptx::tc_fence_before_sync();
       __syncwarp();
@@ -665,7 +725,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
 
-      if (red_any) {
+      if (red_any && !sk_later) {
         if (p.red_axis == FUSEML_AXIS_N) {
           // two warps share a row: each writes its own partial slot
           if (row_ok && ok) {

@@ -64,6 +64,17 @@ struct GemmParams {
   int32_t split_k;
   int32_t kb_per_split;
   float* split_ws;
+  // K-split last wave (CTA pairs, stream_k != 0): tiles [0, T - T % units) run in whole waves, one
+  // tile per unit and wave; each of the remaining R = T % units tiles is cut into S = units / R
+  // equal K slices, one per unit (unit = tile * S + slice), so that the last wave takes 1/S of a
+  // tile's time.  Equal slices keep the units that share operand rows or columns at the same K
+  // position (contiguous ranges of unequal offset, tried first, lose the L2 sharing and run slower
+  // than the ragged wave).  A unit with slice > 0 stores its raw fp32 accumulator to sk_ws[unit]
+  // (per CTA: 128 x BN floats, the split-K piece-major layout) and raises sk_flags[unit]; the
+  // unit with slice 0 adds the later slices to its accumulator in slice order and runs the epilogue.
+  int32_t stream_k;
+  float* sk_ws;
+  uint32_t* sk_flags;   // one per CTA, zeroed by the host before the launch
   int32_t* status;     // device status word (bounded-wait time-outs)
   // Diagnostics (fuseml_sm100_set_diagnostics; both 0 in normal operation): the wall-clock limit
   // of a bounded wait in microseconds (0 = the built-in two seconds), and a host-injected
@@ -88,5 +99,76 @@ __host__ __device__ inline void tile_coords(int32_t t, int32_t tiles_m, int32_t 
   *tm = first_m + (r % rows);
   *tn = r / rows;
 }
+
+// One unit's (CTA's or CTA pair's) walk over its work; the three roles of a CTA run the same walk.
+//   kind 0  a whole tile, K blocks [0, num_kb)
+//   kind 1  the first part of a stream-K tile: this unit finishes the tile after adding the
+//           `after` later parts, which units unit+1 .. unit+after store
+//   kind 2  a later part of a stream-K tile: the raw accumulator goes to the workspace
+//   kind 3  a split-K slice (every CTA has exactly one; folded by splitk_finish_kernel)
+struct WorkItem {
+  int32_t tile, kb0, kb1, kind, after;
+  bool last;            // the unit's last item
+};
+
+struct WorkWalk {
+  int32_t unit, units, num_kb, dp_tiles;
+  int32_t next_dp;      // next whole tile
+  int32_t sk_tile, sk_kb0, sk_kb1, sk_kind, sk_after;   // the unit's K slice of a last-wave tile (sk_tile < 0: none)
+  int32_t splitk_tile, splitk_kb0, splitk_kb1;           // split-K item (kind 3), -1 when taken
+
+  __device__ void init(const GemmParams& p, int32_t unit_, int32_t units_) {
+    unit = unit_; units = units_; num_kb = p.num_kb;
+    splitk_tile = -1; splitk_kb0 = splitk_kb1 = 0;
+    sk_tile = -1; sk_kb0 = sk_kb1 = sk_kind = sk_after = 0;
+    if (p.split_k > 1) {
+      const int32_t slice = unit / p.num_tiles;
+      splitk_tile = unit % p.num_tiles;
+      splitk_kb0 = slice * p.kb_per_split;
+      splitk_kb1 = splitk_kb0 + p.kb_per_split < num_kb ? splitk_kb0 + p.kb_per_split : num_kb;
+      dp_tiles = 0;
+      next_dp = 0;
+      return;
+    }
+    const int32_t rem = p.stream_k ? p.num_tiles % units : 0;
+    const int32_t slices = rem > 0 ? units / rem : 0;       // K slices per last-wave tile
+    dp_tiles = (slices >= 2) ? p.num_tiles - rem : p.num_tiles;
+    next_dp = unit;
+    if (slices >= 2 && unit < rem * slices) {
+      const int32_t per = (num_kb + slices - 1) / slices;
+      const int32_t used = (num_kb + per - 1) / per;          // slices that are not empty
+      const int32_t slice = unit % slices;
+      if (slice < used) {
+        sk_tile = dp_tiles + unit / slices;
+        sk_kb0 = slice * per;
+        sk_kb1 = sk_kb0 + per < num_kb ? sk_kb0 + per : num_kb;
+        sk_kind = (used == 1) ? 0 : (slice == 0 ? 1 : 2);
+        sk_after = slice == 0 ? used - 1 : 0;
+      }
+    }
+  }
+
+  __device__ bool next(WorkItem* w) {
+    if (splitk_tile >= 0) {
+      *w = WorkItem{splitk_tile, splitk_kb0, splitk_kb1, 3, 0, true};
+      splitk_tile = -1;
+      dp_tiles = 0;
+      sk_tile = -1;
+      return true;
+    }
+    if (next_dp < dp_tiles) {
+      const int32_t t = next_dp;
+      next_dp += units;
+      *w = WorkItem{t, 0, num_kb, 0, 0, next_dp >= dp_tiles && sk_tile < 0};
+      return true;
+    }
+    if (sk_tile >= 0) {
+      *w = WorkItem{sk_tile, sk_kb0, sk_kb1, sk_kind, sk_after, true};
+      sk_tile = -1;
+      return true;
+    }
+    return false;
+  }
+};
 
 }  // namespace fuseml

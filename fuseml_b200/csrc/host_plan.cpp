@@ -252,6 +252,23 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
   const int64_t units = std::max(1, props.sm_count / cg);
   plan->grid = static_cast<int32_t>(std::min<int64_t>(tiles, units) * cg);
   if (plan->split_k > 1) plan->grid = static_cast<int32_t>(tiles * plan->split_k);   // one (tile, K slice) per CTA
+  // K-split last wave of CTA-pair launches: with T tiles on U pairs the last wave holds R = T % U
+  // tiles; when R <= U / 2 each of them is cut into S = U / R equal K slices, one per pair, and the
+  // last wave takes 1/S of a tile's time (the later slices pass through the workspace, 256 KB per
+  // pair).  Worth it when the saving, (1 - 1/S) of a wave, is at least 3 % of the launch and the
+  // slices stay long: measured on B200, 4096 x 4096 x 16384 (34 tiles left, 128 K blocks per slice)
+  // gains 10 %, 1024 x 16384 x 4096 (34 tiles left, 32 K blocks per slice) loses 3 % to the pass
+  // of the partial accumulators through the workspace.
+  if (cg == 2 && plan->split_k == 1 && allow_split_k) {
+    const int64_t rem = tiles % units;
+    const int64_t waves = (tiles + units - 1) / units;
+    const int64_t num_kb = k_pad / plan->tile_k;
+    const int64_t slices = rem > 0 ? units / rem : 0;
+    if (slices >= 2 && num_kb >= 64 * slices && (1.0 - 1.0 / static_cast<double>(slices)) / static_cast<double>(waves) >= 0.03) {
+      plan->flags |= FUSEML_PLAN_STREAM_K;
+      plan->grid = static_cast<int32_t>(units * cg);          // every pair takes part in the last wave
+    }
+  }
   // Rasterisation: tiles are walked in groups of group_m tile rows (all columns of one group
   // before the next group).  The group's rows of A stay in L2 while B streams past once per
   // group, so DRAM reads are about bytes(A) + ceil(tiles_m / group_m) * bytes(B): the taller the
@@ -325,6 +342,14 @@ void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, Wo
     // piece-major, see splitk_finish.cuh
     const int64_t tiles = ((d->M + 127) / 128) * ((d->N + plan->tile_n - 1) / plan->tile_n);
     off += align256(static_cast<int64_t>(plan->split_k) * tiles * 128 * plan->tile_n * 4);
+  }
+  if (plan->flags & FUSEML_PLAN_STREAM_K) {
+    const int64_t ctas = plan->grid;
+    w->sk_ws_off = off;
+    off += align256(ctas * 128 * 256 * 4);
+    w->sk_flags_off = off;
+    w->sk_flags_bytes = align256(ctas * 4);
+    off += w->sk_flags_bytes;
   }
   w->total = off;
 }

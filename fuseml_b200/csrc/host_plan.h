@@ -29,6 +29,8 @@ struct WorkspaceLayout {
   int64_t red_sum_off, red_max_off;  // reduction partials
   int64_t partials, len;             // partial arrays are [partials][len]
   int64_t splitk_off;                // split-K: fp32 partial tiles, [split_k][tiles][128 x tile_n]
+  int64_t sk_ws_off, sk_flags_off;   // stream-K: one partial slot (128 x 256 fp32) and one flag per CTA
+  int64_t sk_flags_bytes;
   int64_t total;
 };
 void workspace_layout(const fuseml_gemm_desc_t* d, const fuseml_plan_t* plan, WorkspaceLayout* w);

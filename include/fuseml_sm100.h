@@ -173,6 +173,10 @@ typedef struct {
  * the workspace is reused and only A is expanded.  The caller vouches that neither B nor that
  * part of the workspace was written in between.                                            */
 #define FUSEML_PLAN_B_EXPANSION_VALID 1
+/* plan.flags bit, set by the router for CTA-pair launches whose last wave holds at most half as
+ * many tiles as there are CTA pairs: each of those tiles is cut into equal K slices, one per
+ * pair (later slices pass through the workspace and are added in slice order).             */
+#define FUSEML_PLAN_STREAM_K 2
 
 typedef struct {
   int32_t tile_m;        /* 128                                              */

@@ -172,7 +172,7 @@ def test_a_zeroed_or_garbage_plan_is_a_status_code_not_a_crash(native_lib):
     rc, good = _plan(native_lib, d)
     assert rc == N.OK
     for field, value in (("tile_n", 0), ("tile_n", 48), ("tile_m", 64), ("grid", 0), ("group_m", 0), ("cluster", 3),
-                         ("split_k", 65), ("flags", 2)):
+                         ("split_k", 65), ("flags", 4)):
         bad = N.Plan.from_buffer_copy(good)
         setattr(bad, field, value)
         assert native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(bad)) == -1, field
