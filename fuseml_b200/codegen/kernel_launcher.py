@@ -361,7 +361,7 @@ class KernelLauncher:
                 # (Never while a CUDA graph is being captured: a replay cannot re-check the weight.)
                 tag = (right.data_ptr(), right._version)
                 reuse = p.b_tag.get(stream) == tag and not torch.cuda.is_current_stream_capturing()
-                p.plan.flags = N.PLAN_B_EXPANSION_VALID if reuse else 0
+                p.plan.flags = (p.plan.flags & ~N.PLAN_B_EXPANSION_VALID) | (N.PLAN_B_EXPANSION_VALID if reuse else 0)
                 p.b_tag[stream] = tag
         if p.tune_key is not None and not torch.cuda.is_current_stream_capturing():
             self._tune(p, desc, device, stream)

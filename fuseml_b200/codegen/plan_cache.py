@@ -14,7 +14,7 @@ fuseml/codegen/kernel_generator.py:1067-1172) and re-runs Triton's autotuner in 
 launch it is building towards); here the tuned result itself is what is stored.
 
 File format: ``{"version": 1, "plans": {key: {"tile_n", "cluster", "grid", "group_m",
-"split_k", "us", "candidates"}}}``.  The key names the device, the library build, the problem
+"split_k", "stream_k", "us", "candidates"}}}``.  The key names the device, the library build, the problem
 (M, N, K, dtypes, B layout) and the epilogue signature, so a rebuilt library or another GPU
 never picks up a stale entry.  Writes are atomic (temp file + rename).
 """
@@ -112,11 +112,14 @@ def apply_entry(plan: N.Plan, entry: dict) -> bool:
         return False
     for k, v in vals.items():
         setattr(plan, k, v)
+    if "stream_k" in entry:            # absent in entries written before the flag existed: the router's choice stands
+        plan.flags = (plan.flags & ~N.PLAN_STREAM_K) | (N.PLAN_STREAM_K if entry["stream_k"] else 0)
     return True
 
 
 def entry_of(plan: N.Plan, us: float | None = None, candidates: int = 0) -> dict:
     e = {k: int(getattr(plan, k)) for k in _FIELDS}
+    e["stream_k"] = int(bool(plan.flags & N.PLAN_STREAM_K))
     if us is not None:
         e["us"] = round(float(us), 3)
     e["candidates"] = int(candidates)
@@ -132,7 +135,7 @@ def candidate_plans(base: N.Plan, M: int, Ncols: int, sm_count: int = 148, has_r
         p = N.Plan.from_buffer_copy(base)
         for k, v in kw.items():
             setattr(p, k, v)
-        if all(any(getattr(p, f) != getattr(q, f) for f in _FIELDS) for q in out):
+        if all(any(getattr(p, f) != getattr(q, f) for f in _FIELDS + ("flags",)) for q in out):
             out.append(p)
 
     if base.cluster == 2:
@@ -145,6 +148,9 @@ def candidate_plans(base: N.Plan, M: int, Ncols: int, sm_count: int = 148, has_r
                 add(tile_n=bn, grid=min(tiles, units) * 2)
         for gm in (max(1, base.group_m // 2), min(tiles_m, base.group_m * 2)):
             add(group_m=gm)
+        rem = (tiles_m * -(-Ncols // base.tile_n)) % units
+        if 0 < rem <= units // 2 and not has_reduction:       # the last wave cut into K slices, or not
+            add(flags=base.flags ^ N.PLAN_STREAM_K)
     elif base.split_k > 1 and not has_reduction:
         for sk in (max(2, base.split_k // 2), min(32, base.split_k * 2)):
             tiles = -(-Ncols // base.tile_n)

@@ -298,6 +298,16 @@ def test_plan_cache_round_trip_and_candidates(tmp_path):
     # 1024 rows x 16384 columns: 256 tiles are 3.46 waves of 74 pairs; 224-wide tiles fill four waves
     shard = pc.candidate_plans(base, 1024, 16384)
     assert shard[0].tile_n == 256 and 224 in [c.tile_n for c in shard]
+    # its last wave holds 34 tiles (at most half of the pairs): the K-split last wave is tried too,
+    # and the choice survives the file (the per-call expansion bit does not)
+    toggled = [c for c in shard if c.flags & N.PLAN_STREAM_K]
+    assert len(toggled) == 1 and toggled[0].tile_n == 256
+    toggled[0].flags |= N.PLAN_B_EXPANSION_VALID
+    entry = pc.entry_of(toggled[0], 1.0, 1)
+    restored = N.Plan()
+    assert entry["stream_k"] == 1 and pc.apply_entry(restored, entry) and restored.flags == N.PLAN_STREAM_K
+    entry.pop("stream_k")
+    assert pc.apply_entry(restored, entry) and restored.flags == N.PLAN_STREAM_K      # older entry: flag untouched
     # 8192 rows: 27.7 waves, nothing to gain from narrower tiles; only the group size varies
     full = pc.candidate_plans(base, 8192, 16384)
     assert {c.tile_n for c in full} == {256} and len(full) == 3
