@@ -104,6 +104,12 @@ class Plan(C.Structure):
         return {name: getattr(self, name) for name, _ in self._fields_}
 
 
+class WorkItem(C.Structure):
+    """``fuseml_work_item_t``: one entry of a unit's schedule (``fuseml_sm100_schedule``)."""
+    _fields_ = [("tile", C.c_int32), ("kb0", C.c_int32), ("kb1", C.c_int32), ("kind", C.c_int32),
+                ("after", C.c_int32), ("slot", C.c_int32)]
+
+
 class DeviceProps(C.Structure):
     _fields_ = [
         ("sm_count", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
@@ -119,6 +125,7 @@ EXPORTS = (
     "fuseml_sm100_strerror", "fuseml_sm100_abi_version",
     "fuseml_sm100_gemm_epilogue_noalloc", "fuseml_sm100_noalloc_scratch_bytes",
     "fuseml_sm100_set_diagnostics", "fuseml_sm100_mlp_small", "fuseml_sm100_mlp_small_workspace_bytes",
+    "fuseml_sm100_schedule",
 )
 
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfuseml_sm100.so"
@@ -161,6 +168,9 @@ def _declare(lib: C.CDLL) -> None:
     lib.fuseml_sm100_set_diagnostics.argtypes = [C.c_int64, C.c_int32]
     lib.fuseml_sm100_device_status.restype = C.c_int
     lib.fuseml_sm100_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    lib.fuseml_sm100_schedule.restype = C.c_int32
+    lib.fuseml_sm100_schedule.argtypes = [C.POINTER(GemmDesc), C.POINTER(Plan), C.c_int32, C.POINTER(WorkItem),
+                                          C.c_int32, C.POINTER(C.c_int32)]
 
 
 def load(path: os.PathLike | str | None = None) -> C.CDLL:

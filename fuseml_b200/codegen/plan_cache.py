@@ -149,8 +149,11 @@ def candidate_plans(base: N.Plan, M: int, Ncols: int, sm_count: int = 148, has_r
         for gm in (max(1, base.group_m // 2), min(tiles_m, base.group_m * 2)):
             add(group_m=gm)
         rem = (tiles_m * -(-Ncols // base.tile_n)) % units
-        if 0 < rem <= units // 2 and not has_reduction:       # the last wave cut into K slices, or not
-            add(flags=base.flags ^ N.PLAN_STREAM_K)
+        if 0 < rem and not has_reduction:                     # the last wave shared by K ranges, or not
+            if base.flags & N.PLAN_STREAM_K:
+                add(flags=base.flags & ~N.PLAN_STREAM_K)
+            else:                                             # every pair takes part in the last wave
+                add(flags=base.flags | N.PLAN_STREAM_K, grid=units * 2)
     elif base.split_k > 1 and not has_reduction:
         for sk in (max(2, base.split_k // 2), min(32, base.split_k * 2)):
             tiles = -(-Ncols // base.tile_n)

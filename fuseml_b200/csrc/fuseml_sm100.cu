@@ -854,6 +854,48 @@ static int noalloc_scratch_address(void** out) {
 
 int64_t fuseml_sm100_noalloc_scratch_bytes(void) { return kNoAllocScratchBytes; }
 
+int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan_in, int32_t unit,
+                              fuseml_work_item_t* items, int32_t max_items, int32_t* n_units) {
+  if (plan_in == nullptr || (items == nullptr && max_items > 0)) return -FUSEML_E_NULL;
+  int rc = validate_desc(desc);
+  if (rc != FUSEML_OK) return -rc;
+  rc = check_plan(plan_in);
+  if (rc != FUSEML_OK) return -rc;
+  // the geometry of fuseml_sm100_gemm_epilogue
+  const bool f32 = desc->ab_dtype == FUSEML_F32;
+  const int64_t K = f32 ? 3 * desc->K : desc->K;
+  const int BK = f32 ? 32 : 64;
+  const int CGr = plan_in->cluster;
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.tiles_m = static_cast<int32_t>((desc->M + kTileM * CGr - 1) / (kTileM * CGr));
+  p.tiles_n = static_cast<int32_t>((desc->N + plan_in->tile_n - 1) / plan_in->tile_n);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.num_kb = static_cast<int32_t>((K + BK - 1) / BK);
+  int32_t units;
+  if (plan_in->split_k > 1) {
+    p.kb_per_split = (p.num_kb + plan_in->split_k - 1) / plan_in->split_k;
+    p.split_k = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    units = p.num_tiles * p.split_k;
+  } else if (plan_in->flags & FUSEML_PLAN_STREAM_K) {
+    p.stream_k = 1;
+    units = plan_in->grid / CGr;
+  } else {
+    units = std::min(plan_in->grid, p.num_tiles * CGr) / CGr;
+  }
+  if (n_units != nullptr) *n_units = units;
+  if (units < 1 || unit < 0 || unit >= units) return -FUSEML_E_PLAN;
+  WorkWalk walk;
+  walk.init(p, unit, units);
+  WorkItem w;
+  int32_t n = 0;
+  while (walk.next(&w)) {
+    if (n < max_items) items[n] = fuseml_work_item_t{w.tile, w.kb0, w.kb1, w.kind, w.after, w.slot};
+    ++n;
+  }
+  return n;
+}
+
 int fuseml_sm100_gemm_epilogue_noalloc(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan_in,
                                        void* cuda_stream) {
   int rc = validate_desc(desc);

@@ -50,7 +50,7 @@ enum : int32_t {
 //   [6] wall clock (ns) at kernel entry                [7] wall clock (ns) just before the CTA exits
 //   [8] ... after set-up (barriers, TMEM, cluster sync) [9] ... when the MMA thread has issued everything
 //   [10] ... when epilogue warp 2 is done               [11] ... after the tear-down barriers
-//   [12..15] epilogue warp 2, cycles: TMEM load | epilogue program | store / tile write | unused
+//   [12..15] epilogue warp 2, cycles: TMEM load | epilogue program | store / tile write | waiting for K-split parts
 #ifdef FUSEML_STALL_COUNTERS
 __device__ unsigned long long g_stall[1024][16];
 #define FUSEML_STALL_T0() const long long stall_t0 = clock64()
@@ -514,8 +514,6 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     // warp-level store writes 32 consecutive 16-byte pieces (512 contiguous bytes) instead of
     // 32 pieces in 32 different rows, and splitk_finish_kernel reads them back the same way.
     float* const split_tile = splitk ? p.split_ws + static_cast<int64_t>(k_slice) * p.num_tiles * (kTileM * bn) : nullptr;
-    // Stream-K: this CTA's slot for the raw accumulator of a later part, and its flag
-    float* const sk_mine = p.stream_k ? p.sk_ws + (static_cast<int64_t>(unit) * CG + cta_rank) * (kTileM * BN) : nullptr;
     WorkWalk walk;
     walk.init(p, unit, num_units);
     WorkItem w;
@@ -567,10 +565,13 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         ok = false;
       }
       if (sk_first && ok) {
-        // the later parts of this tile were stored by the next `after` units, normally long ago
-        // (a unit works on its later part first); bounded wait on their flags all the same
-        for (int32_t j = 1; j <= w.after && ok; ++j) {
-          const volatile uint32_t* flag = p.sk_flags + (static_cast<int64_t>(unit + j) * CG + cta_rank);
+#ifdef FUSEML_STALL_COUNTERS
+        const long long flag_t0 = clock64();
+#endif
+        // the later parts of this tile lie in `after` consecutive workspace slots, normally
+        // complete by now (their K ranges are no longer than this one); bounded wait on the flags
+        for (int32_t j = 0; j < w.after && ok; ++j) {
+          const volatile uint32_t* flag = p.sk_flags + (static_cast<int64_t>(w.slot + j) * CG + cta_rank);
           const uint64_t t0 = ptx::globaltimer_ns();
           while (*flag == 0u) {
             __nanosleep(64);
@@ -583,6 +584,9 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           }
         }
         __threadfence();
+#ifdef FUSEML_STALL_COUNTERS
+        st_tail += clock64() - flag_t0;
+#endif
       }
 #pragma unroll 1
       for (int c = half; (ok || staged_io) && c < bn / CH; c += kEpiSplit) {
@@ -618,17 +622,19 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           const long long c1 = clock64();
 #endif
           if (sk_first) {
-            // later parts in unit order: the sum does not depend on which unit finished first
-            for (int32_t j = 1; j <= w.after; ++j) {
-              const float4* src = reinterpret_cast<const float4*>(p.sk_ws + (static_cast<int64_t>(unit + j) * CG + cta_rank) * (kTileM * BN)) +
+            // later parts in slot order: the sum does not depend on which unit finished first
+            for (int32_t j = 0; j < w.after; ++j) {
+              const float4* src = reinterpret_cast<const float4*>(p.sk_ws + (static_cast<int64_t>(w.slot + j) * CG + cta_rank) * (kTileM * BN)) +
                                   static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
+              float4 x[CH / 4];
+#pragma unroll
+              for (int i = 0; i < CH / 4; ++i) x[i] = __ldcg(src + i * kTileM);
 #pragma unroll
               for (int i = 0; i < CH / 4; ++i) {
-                const float4 x = __ldcg(src + i * kTileM);
-                v[4 * i + 0] += x.x;
-                v[4 * i + 1] += x.y;
-                v[4 * i + 2] += x.z;
-                v[4 * i + 3] += x.w;
+                v[4 * i + 0] += x[i].x;
+                v[4 * i + 1] += x[i].y;
+                v[4 * i + 2] += x[i].z;
+                v[4 * i + 3] += x[i].w;
               }
             }
           }
@@ -637,7 +643,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           const long long c2 = clock64();
 #endif
           if (sk_later) {
-            float4* dst = reinterpret_cast<float4*>(sk_mine) + static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
+            float4* dst = reinterpret_cast<float4*>(p.sk_ws + (static_cast<int64_t>(w.slot) * CG + cta_rank) * (kTileM * BN)) +
+                          static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
 #pragma unroll
             for (int i = 0; i < CH / 4; ++i)
               dst[i * kTileM] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -706,12 +713,14 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
         }
       }
       if (sk_later) {
-        // publish this part: every thread's stores, then one flag per CTA
-        __threadfence();
+        // publish this part: the barrier orders every epilogue thread's stores before thread
+        // 64's fence, and the fence (cumulative) orders them before the flag for whoever reads
+        // the flag and fences in turn.  One fence per CTA: a fence per thread waits for the
+        // thread's own stores under a saturated memory system, 256 times over.
         asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
         if (threadIdx.x == 64 && ok) {
-          *reinterpret_cast<volatile uint32_t*>(p.sk_flags + (static_cast<int64_t>(unit) * CG + cta_rank)) = 1u;
           __threadfence();
+          *reinterpret_cast<volatile uint32_t*>(p.sk_flags + (static_cast<int64_t>(w.slot) * CG + cta_rank)) = 1u;
         }
       }
       // accumulator drained: hand the TMEM buffer back to the (leader's) MMA thread

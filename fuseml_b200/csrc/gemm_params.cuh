@@ -64,14 +64,14 @@ struct GemmParams {
   int32_t split_k;
   int32_t kb_per_split;
   float* split_ws;
-  // K-split last wave (CTA pairs, stream_k != 0): tiles [0, T - T % units) run in whole waves, one
-  // tile per unit and wave; each of the remaining R = T % units tiles is cut into S = units / R
-  // equal K slices, one per unit (unit = tile * S + slice), so that the last wave takes 1/S of a
-  // tile's time.  Equal slices keep the units that share operand rows or columns at the same K
-  // position (contiguous ranges of unequal offset, tried first, lose the L2 sharing and run slower
-  // than the ragged wave).  A unit with slice > 0 stores its raw fp32 accumulator to sk_ws[unit]
-  // (per CTA: 128 x BN floats, the split-K piece-major layout) and raises sk_flags[unit]; the
-  // unit with slice 0 adds the later slices to its accumulator in slice order and runs the epilogue.
+  // K-split last wave (CTA pairs, stream_k != 0): the tiles of a ragged last wave are shared
+  // between all units by K ranges (see WorkWalk).  A unit that computes a later part of a tile
+  // stores its raw fp32 accumulator to workspace slot s (per CTA: 128 x BN floats at
+  // sk_ws[s * CG + rank], the split-K piece-major layout) and raises sk_flags[s * CG + rank];
+  // the unit that owns the tile adds the parts to its accumulator in slot order and runs the
+  // epilogue.  (Contiguous K ranges of equal length for every unit, tried first, put the units
+  // at different K positions, lose the sharing of operands through L2 and run slower than the
+  // ragged wave.)
   int32_t stream_k;
   float* sk_ws;
   uint32_t* sk_flags;   // one per CTA, zeroed by the host before the launch
@@ -102,25 +102,40 @@ __host__ __device__ inline void tile_coords(int32_t t, int32_t tiles_m, int32_t 
 
 // One unit's (CTA's or CTA pair's) walk over its work; the three roles of a CTA run the same walk.
 //   kind 0  a whole tile, K blocks [0, num_kb)
-//   kind 1  the first part of a stream-K tile: this unit finishes the tile after adding the
-//           `after` later parts, which units unit+1 .. unit+after store
-//   kind 2  a later part of a stream-K tile: the raw accumulator goes to the workspace
+//   kind 1  the first part of a K-split tile: this unit finishes the tile after adding the
+//           `after` later parts, which other units left in workspace slots slot .. slot+after-1
+//   kind 2  a later part of a K-split tile: the raw accumulator goes to workspace slot `slot`
 //   kind 3  a split-K slice (every CTA has exactly one; folded by splitk_finish_kernel)
+//
+// K-split last wave (GemmParams::stream_k): T tiles on U units leave R = T % U tiles for the last
+// wave; the whole waves before it are walked as usual.
+//   R <= U / 2  every last-wave tile is cut into S = U / R equal K slices, one per unit; the unit
+//               with slice 0 finishes the tile (slot of a later slice = its unit index).
+//   R >  U / 2  owner units 0..R-1 take K blocks [0, num_kb - L) of their tile, where
+//               L = 3/4 num_kb (U - R) / U; the R L blocks left over form one stream in tile order that
+//               the U - R helper units share in equal contiguous runs.  A run crosses tile
+//               boundaries, so a helper walks several short parts; the part of tile t done by
+//               helper h goes to slot t + h (parts are ordered in both, so the sum is unique), and
+//               a tile's leftover lies in at most two helpers' runs.
+// Either way every unit's last-wave work starts at the same time and takes about the same time,
+// owners walk K in step (they share B through L2), and sums run in slot order.
 struct WorkItem {
-  int32_t tile, kb0, kb1, kind, after;
+  int32_t tile, kb0, kb1, kind, after, slot;
   bool last;            // the unit's last item
 };
 
 struct WorkWalk {
   int32_t unit, units, num_kb, dp_tiles;
   int32_t next_dp;      // next whole tile
-  int32_t sk_tile, sk_kb0, sk_kb1, sk_kind, sk_after;   // the unit's K slice of a last-wave tile (sk_tile < 0: none)
-  int32_t splitk_tile, splitk_kb0, splitk_kb1;           // split-K item (kind 3), -1 when taken
+  int32_t sk_tile, sk_kb0, sk_kb1, sk_kind, sk_after, sk_slot;   // the unit's one part of a last-wave tile (sk_tile < 0: none)
+  int32_t hp_pos, hp_end, hp_len, hp_own, hp_index;              // a helper's run of left-over K blocks (hp_pos >= hp_end: none)
+  int32_t splitk_tile, splitk_kb0, splitk_kb1;                   // split-K item (kind 3), -1 when taken
 
-  __device__ void init(const GemmParams& p, int32_t unit_, int32_t units_) {
+  __host__ __device__ void init(const GemmParams& p, int32_t unit_, int32_t units_) {
     unit = unit_; units = units_; num_kb = p.num_kb;
     splitk_tile = -1; splitk_kb0 = splitk_kb1 = 0;
-    sk_tile = -1; sk_kb0 = sk_kb1 = sk_kind = sk_after = 0;
+    sk_tile = -1; sk_kb0 = sk_kb1 = sk_kind = sk_after = sk_slot = 0;
+    hp_pos = hp_end = hp_len = hp_own = hp_index = 0;
     if (p.split_k > 1) {
       const int32_t slice = unit / p.num_tiles;
       splitk_tile = unit % p.num_tiles;
@@ -132,25 +147,54 @@ struct WorkWalk {
     }
     const int32_t rem = p.stream_k ? p.num_tiles % units : 0;
     const int32_t slices = rem > 0 ? units / rem : 0;       // K slices per last-wave tile
-    dp_tiles = (slices >= 2) ? p.num_tiles - rem : p.num_tiles;
+    dp_tiles = p.num_tiles;
     next_dp = unit;
-    if (slices >= 2 && unit < rem * slices) {
-      const int32_t per = (num_kb + slices - 1) / slices;
-      const int32_t used = (num_kb + per - 1) / per;          // slices that are not empty
-      const int32_t slice = unit % slices;
-      if (slice < used) {
-        sk_tile = dp_tiles + unit / slices;
-        sk_kb0 = slice * per;
-        sk_kb1 = sk_kb0 + per < num_kb ? sk_kb0 + per : num_kb;
-        sk_kind = (used == 1) ? 0 : (slice == 0 ? 1 : 2);
-        sk_after = slice == 0 ? used - 1 : 0;
+    if (slices >= 2) {
+      dp_tiles = p.num_tiles - rem;
+      if (unit < rem * slices) {
+        const int32_t per = (num_kb + slices - 1) / slices;
+        const int32_t used = (num_kb + per - 1) / per;          // slices that are not empty
+        const int32_t slice = unit % slices;
+        if (slice < used) {
+          sk_tile = dp_tiles + unit / slices;
+          sk_kb0 = slice * per;
+          sk_kb1 = sk_kb0 + per < num_kb ? sk_kb0 + per : num_kb;
+          sk_kind = (used == 1) ? 0 : (slice == 0 ? 1 : 2);
+          sk_after = slice == 0 ? used - 1 : 0;
+          sk_slot = slice == 0 ? unit + 1 : unit;
+        }
+      }
+    } else if (slices == 1 && rem < units) {
+      const int32_t idle = units - rem;
+      // L: 3/4 of the even share.  A helper's K blocks come slower than an owner's (its operands
+      // are shared with nobody through L2; measured 0.41 against 0.36 us per block) and each of its
+      // parts ends with a store of the raw accumulator.
+      const int32_t left = static_cast<int32_t>(static_cast<int64_t>(num_kb) * idle * 3 / (static_cast<int64_t>(units) * 4));
+      if (left >= 1) {
+        dp_tiles = p.num_tiles - rem;
+        const int32_t run = (rem * left + idle - 1) / idle;       // K blocks per helper (>= left, as rem > idle)
+        if (unit < rem) {
+          const int32_t h0 = unit * left / run, h1 = ((unit + 1) * left - 1) / run;
+          sk_tile = dp_tiles + unit;
+          sk_kb0 = 0;
+          sk_kb1 = num_kb - left;
+          sk_kind = 1;
+          sk_after = h1 - h0 + 1;
+          sk_slot = unit + h0;
+        } else {
+          hp_index = unit - rem;
+          hp_len = left;
+          hp_own = num_kb - left;
+          hp_pos = hp_index * run;
+          hp_end = hp_pos + run < rem * left ? hp_pos + run : rem * left;
+        }
       }
     }
   }
 
-  __device__ bool next(WorkItem* w) {
+  __host__ __device__ bool next(WorkItem* w) {
     if (splitk_tile >= 0) {
-      *w = WorkItem{splitk_tile, splitk_kb0, splitk_kb1, 3, 0, true};
+      *w = WorkItem{splitk_tile, splitk_kb0, splitk_kb1, 3, 0, 0, true};
       splitk_tile = -1;
       dp_tiles = 0;
       sk_tile = -1;
@@ -159,12 +203,19 @@ struct WorkWalk {
     if (next_dp < dp_tiles) {
       const int32_t t = next_dp;
       next_dp += units;
-      *w = WorkItem{t, 0, num_kb, 0, 0, next_dp >= dp_tiles && sk_tile < 0};
+      *w = WorkItem{t, 0, num_kb, 0, 0, 0, next_dp >= dp_tiles && sk_tile < 0 && hp_pos >= hp_end};
       return true;
     }
     if (sk_tile >= 0) {
-      *w = WorkItem{sk_tile, sk_kb0, sk_kb1, sk_kind, sk_after, true};
+      *w = WorkItem{sk_tile, sk_kb0, sk_kb1, sk_kind, sk_after, sk_slot, true};
       sk_tile = -1;
+      return true;
+    }
+    if (hp_pos < hp_end) {
+      const int32_t t = hp_pos / hp_len;
+      const int32_t stop = hp_end < (t + 1) * hp_len ? hp_end : (t + 1) * hp_len;
+      *w = WorkItem{dp_tiles + t, hp_own + (hp_pos - t * hp_len), hp_own + (stop - t * hp_len), 2, 0, t + hp_index, stop == hp_end};
+      hp_pos = stop;
       return true;
     }
     return false;

@@ -252,13 +252,17 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
   const int64_t units = std::max(1, props.sm_count / cg);
   plan->grid = static_cast<int32_t>(std::min<int64_t>(tiles, units) * cg);
   if (plan->split_k > 1) plan->grid = static_cast<int32_t>(tiles * plan->split_k);   // one (tile, K slice) per CTA
-  // K-split last wave of CTA-pair launches: with T tiles on U pairs the last wave holds R = T % U
-  // tiles; when R <= U / 2 each of them is cut into S = U / R equal K slices, one per pair, and the
-  // last wave takes 1/S of a tile's time (the later slices pass through the workspace, 256 KB per
-  // pair).  Worth it when the saving, (1 - 1/S) of a wave, is at least 3 % of the launch and the
-  // slices stay long: measured on B200, 4096 x 4096 x 16384 (34 tiles left, 128 K blocks per slice)
-  // gains 10 %, 1024 x 16384 x 4096 (34 tiles left, 32 K blocks per slice) loses 3 % to the pass
-  // of the partial accumulators through the workspace.
+  // K-split last wave of CTA-pair launches (the walk itself is WorkWalk in gemm_params.cuh): with
+  // T tiles on U pairs the last wave holds R = T % U tiles.  R <= U / 2: each is cut into S = U / R
+  // equal K slices, one per pair, and the wave takes 1/S of a tile's time; the later slices pass
+  // through the workspace (256 KB per pair).  Chosen when the saving, (1 - 1/S) of a wave, is at
+  // least 3 % of the launch and the slices stay long: measured on B200, 4096 x 4096 x 16384
+  // (34 tiles left, 128 K blocks per slice) gains 10 %, 1024 x 16384 x 4096 (34 tiles left, 32 K
+  // blocks per slice) loses 3 % to the pass of the partial accumulators through the workspace.
+  // R > U / 2 (the idle pairs take the K tails of the others' tiles) is never chosen here: the
+  // helpers' short parts and the owners' wait for them cost what the shorter wave saves
+  // (2048 x 4096 x 16384, 54 tiles left: 198 us either way; 1024 x 4096 x 16384, 64 lone tiles:
+  // 110 us against 99 us); a caller or the plan tuner may still set the flag.
   if (cg == 2 && plan->split_k == 1 && allow_split_k) {
     const int64_t rem = tiles % units;
     const int64_t waves = (tiles + units - 1) / units;

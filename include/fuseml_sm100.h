@@ -316,6 +316,23 @@ int fuseml_sm100_reduce_tail(const void* x, int32_t dtype, int64_t M, int64_t N,
  * Used by the tests of the time-out path; nothing on the GPU faults or traps. */
 int fuseml_sm100_set_diagnostics(int64_t wait_limit_us, int32_t drop_last_load);
 
+/* No counterpart in the reference (its Triton grid is one program per tile).  The work one unit
+ * (a CTA, or a CTA pair when plan->cluster is 2) of a launch of `desc` under `plan` walks through,
+ * in order: whole tiles, and with split-K or FUSEML_PLAN_STREAM_K parts of tiles.  Host
+ * arithmetic only, no device needed: the kernel runs the same code.  `*n_units` (may be null)
+ * receives the number of units of the launch.  Writes at most `max_items` entries and returns
+ * the number of items the unit has (>= 0), or -FUSEML_E_* for a bad descriptor, plan or unit. */
+typedef struct {
+  int32_t tile;        /* tile index in rasterisation order                                      */
+  int32_t kb0, kb1;    /* K blocks [kb0, kb1) of the tile                                         */
+  int32_t kind;        /* 0 whole tile; 1 first part, finishes the tile after adding `after`
+                          parts from workspace slots slot..slot+after-1; 2 later part, stored to
+                          workspace slot `slot`; 3 split-K slice                                   */
+  int32_t after, slot;
+} fuseml_work_item_t;
+int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan, int32_t unit,
+                              fuseml_work_item_t* items, int32_t max_items, int32_t* n_units);
+
 /* Where a bounded wait gave up (the value fuseml_sm100_device_status returns in *status_out). */
 enum {
   FUSEML_WHERE_PRODUCER_EMPTY = 0x201,   /* TMA producer: a ring stage never became free      */

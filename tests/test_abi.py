@@ -179,6 +179,105 @@ def test_a_zeroed_or_garbage_plan_is_a_status_code_not_a_crash(native_lib):
         assert native_lib.fuseml_sm100_gemm_epilogue_noalloc(C.byref(d), C.byref(bad), None) == N.E_PLAN, field
 
 
+def _schedule(native_lib, d, p):
+    """Every unit's work items: {unit: [WorkItem, ...]}."""
+    n_units = C.c_int32(0)
+    buf = (N.WorkItem * 64)()
+    out = {}
+    n = native_lib.fuseml_sm100_schedule(C.byref(d), C.byref(p), 0, buf, 64, C.byref(n_units))
+    assert n >= 0
+    for u in range(n_units.value):
+        n = native_lib.fuseml_sm100_schedule(C.byref(d), C.byref(p), u, buf, 64, None)
+        assert 0 <= n <= 64
+        out[u] = [N.WorkItem.from_buffer_copy(buf[i]) for i in range(n)]
+    return out
+
+
+@pytest.mark.parametrize("M,Nn,K,grid", [
+    (4096, 4096, 16384, 148),     # 256 tiles on 74 pairs: 34 left, two equal K slices each
+    (1024, 4096, 16384, 148),     # 64 tiles: no whole wave, 10 helper pairs take the K tails
+    (2048, 4096, 16384, 148),     # 128 tiles: one whole wave, then 54 owners and 20 helpers
+    (8192, 4096, 16384, 148),     # 512 tiles: 68 left, 6 helpers
+    (600, 1000, 4096, 10),        # 12 tiles on 5 pairs, ragged edges
+    (520, 1100, 2048, 14),        # 15 tiles on 7 pairs: 1 left, seven slices
+    (2048, 2048, 1024, 18),       # 64 tiles on 9 pairs: 1 left, 16 K blocks in 8 slices
+    (1280, 256, 64 * 7, 16),      # 5 tiles on 8 pairs, 7 K blocks: runs of helpers end early
+    (1536, 256, 64 * 3, 16),      # 6 tiles on 8 pairs, 3 K blocks: nothing left over, whole tiles
+    (256, 256 * 9, 64 * 40, 20),  # 9 tiles on 10 pairs: one helper adds to every tile
+])
+def test_k_split_schedule_covers_every_k_block_once(native_lib, M, Nn, K, grid):
+    """The walk the kernel runs, executed on the host: with FUSEML_PLAN_STREAM_K every K block of
+    every tile belongs to exactly one work item, each tile has exactly one finishing item, the
+    workspace slots of the later parts are distinct, lie inside the workspace, and are exactly the
+    ones the finishing item of their tile reads; units carry about the same number of K blocks."""
+    d = _desc(M, Nn, K)
+    rc, p = _plan(native_lib, d)
+    assert rc == N.OK and p.cluster == 2
+    p.grid = grid
+    p.flags |= N.PLAN_STREAM_K
+    units = grid // 2
+    tiles = -(-M // 256) * -(-Nn // p.tile_n)
+    num_kb = -(-K // 64)
+    sched = _schedule(native_lib, d, p)
+    assert len(sched) == units
+    cover = {t: [0] * num_kb for t in range(tiles)}
+    finishers, parts, load = {}, {}, []
+    for u, items in sched.items():
+        load.append(sum(w.kb1 - w.kb0 for w in items))
+        for w in items:
+            assert 0 <= w.tile < tiles and 0 <= w.kb0 < w.kb1 <= num_kb and w.kind in (0, 1, 2)
+            for kb in range(w.kb0, w.kb1):
+                cover[w.tile][kb] += 1
+            if w.kind == 2:
+                assert 0 <= w.slot < units and w.slot not in parts
+                parts[w.slot] = w.tile
+            else:
+                assert w.tile not in finishers
+                finishers[w.tile] = w
+                assert (w.kind == 0) == (w.after == 0) and (w.kind == 0) <= (w.kb1 - w.kb0 == num_kb)
+    assert all(c == [1] * num_kb for c in cover.values())
+    assert sorted(finishers) == list(range(tiles))
+    read = {}
+    for t, w in finishers.items():
+        for s in range(w.slot, w.slot + w.after):
+            assert s not in read
+            read[s] = t
+    assert read == parts
+    whole = tiles // units * num_kb
+    rem = tiles % units
+    if rem == 0:
+        last = 0
+    elif rem <= units // 2:
+        last = -(-num_kb // (units // rem))                       # equal slices
+    else:
+        last = num_kb - num_kb * (units - rem) * 3 // (units * 4)  # an owner's part; helpers' runs are no longer
+    assert max(load) - whole <= last
+    ws = native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(p))
+    assert ws >= grid * 128 * 256 * 4 + grid * 4
+    # without the flag: whole tiles only, unit u takes tiles u, u + units, ...
+    p.flags &= ~N.PLAN_STREAM_K
+    plain = _schedule(native_lib, d, p)
+    assert all(w.kind == 0 and w.tile % len(plain) == u for u, items in plain.items() for w in items)
+    assert sum(len(v) for v in plain.values()) == tiles
+
+
+def test_schedule_of_a_split_k_plan_and_bad_arguments(native_lib):
+    d = _desc(128, 512, 2048)
+    rc, p = _plan(native_lib, d)
+    assert rc == N.OK and p.split_k == 4
+    sched = _schedule(native_lib, d, p)
+    assert len(sched) == 2 * 4                        # two 256-column tiles, four K slices each
+    assert sorted((w.tile, w.kb0, w.kb1) for items in sched.values() for w in items) == \
+        [(t, 8 * s, 8 * s + 8) for t in range(2) for s in range(4)]
+    assert all(len(items) == 1 and items[0].kind == 3 for items in sched.values())
+    buf = (N.WorkItem * 1)()
+    assert native_lib.fuseml_sm100_schedule(C.byref(d), C.byref(p), 8, buf, 1, None) == -N.E_PLAN
+    assert native_lib.fuseml_sm100_schedule(C.byref(d), C.byref(p), -1, buf, 1, None) == -N.E_PLAN
+    assert native_lib.fuseml_sm100_schedule(C.byref(d), None, 0, buf, 1, None) == -N.E_NULL
+    assert native_lib.fuseml_sm100_schedule(C.byref(d), C.byref(N.Plan()), 0, buf, 1, None) == -N.E_PLAN
+    assert native_lib.fuseml_sm100_schedule(C.byref(d), C.byref(p), 0, None, 0, None) == 1   # count only
+
+
 def test_struct_layout_matches_header():
     assert C.sizeof(N.EpiOp) == 16
     assert C.sizeof(N.Operand) == 32

@@ -733,6 +733,11 @@ STREAM_K_CASES = [
     (600, 4096, 1000, 10, "res", ()),               # 12 tiles on 5 pairs: 2 tiles left, two slices each; ragged edges
     (520, 2048, 1100, 14, "gelu", ("sum", "max")),  # 15 tiles on 7 pairs: 1 tile left in seven slices; row reductions
     (2048, 1024, 2048, 18, "relu", ("mean",)),      # 64 tiles on 9 pairs: 1 tile left, 16 K blocks in 8 slices, one pair idle
+    # more than half of the pairs hold a tile of the last wave: the others take the K tails
+    (1024, 16384, 4096, None, "res", ()),           # 64 tiles, no whole wave: 10 helpers, seven short parts each
+    (2048, 16384, 4096, None, "res", ()),           # 128 tiles: a whole wave, then 54 owners and 20 helpers
+    (1280, 448, 256, 16, "gelu", ("sum", "max")),   # 5 tiles on 8 pairs, 7 K blocks: two helpers, one pair idle; reductions
+    (200, 2560, 2200, 20, "res", ()),               # 9 tiles on 10 pairs: one helper adds 4 K blocks to every tile; ragged
 ]
 
 
