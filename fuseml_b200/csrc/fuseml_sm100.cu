@@ -484,7 +484,8 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
     }
   }
 
-  const bool stream_k = (plan.flags & FUSEML_PLAN_STREAM_K) != 0;
+  // (programs with a second value register run whole tiles only: see kStreamK in the kernel)
+  const bool stream_k = (plan.flags & FUSEML_PLAN_STREAM_K) != 0 && !p.uses_saved;
   int grid = stream_k ? plan.grid : std::min(plan.grid, p.num_tiles * CGr);
   if (stream_k) {
     p.stream_k = 1;
@@ -854,6 +855,17 @@ static int noalloc_scratch_address(void** out) {
 
 int64_t fuseml_sm100_noalloc_scratch_bytes(void) { return kNoAllocScratchBytes; }
 
+// whether the program, after the diamond rewrite, still keeps a second value register
+static bool program_uses_saved(const fuseml_gemm_desc_t* desc) {
+  fuseml_epi_op_t ops[FUSEML_MAX_EPI_OPS];
+  const int n = fuse_diamonds(desc->ops, desc->n_ops, ops);
+  for (int i = 0; i < n; ++i) {
+    const int32_t oc = ops[i].opcode;
+    if (oc == FUSEML_OP_SAVE || oc == FUSEML_OP_SWAP || oc == FUSEML_OP_ADD_SAVED || oc == FUSEML_OP_MUL_SAVED) return true;
+  }
+  return false;
+}
+
 int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan_in, int32_t unit,
                               fuseml_work_item_t* items, int32_t max_items, int32_t* n_units) {
   if (plan_in == nullptr || (items == nullptr && max_items > 0)) return -FUSEML_E_NULL;
@@ -877,7 +889,7 @@ int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_
     p.kb_per_split = (p.num_kb + plan_in->split_k - 1) / plan_in->split_k;
     p.split_k = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
     units = p.num_tiles * p.split_k;
-  } else if (plan_in->flags & FUSEML_PLAN_STREAM_K) {
+  } else if ((plan_in->flags & FUSEML_PLAN_STREAM_K) && !program_uses_saved(desc)) {
     p.stream_k = 1;
     units = plan_in->grid / CGr;
   } else {

@@ -141,6 +141,10 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
   using L = Smem<BN, STAGES, CG>;
   constexpr bool B_MN = LAYOUT >= 1;
   constexpr bool A_MN = LAYOUT == 2;
+  // the K-split last wave exists for CTA pairs with eight epilogue warps whose program keeps no
+  // second value register (the host never asks the other instances for it: their registers
+  // have no room for the walk's extra state)
+  constexpr bool kStreamK = (CG == 2 && EW == 8 && PROG != epi::kProgGenericSaved);
   const bool tf32 = p.fmt == 2;
   const int32_t BK = tf32 ? 32 : 64;             // elements per 128-byte stage row
   constexpr int kKSteps = 4;                      // MMAs per stage: 32 bytes of K each (16 x 16-bit or 8 x tf32)
@@ -259,7 +263,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const uint64_t pol_normal = ptx::policy_evict_normal();
       long long st_empty = 0;
       WorkWalk walk;
-      walk.init(p, unit, num_units);
+      walk.template init<kStreamK>(p, unit, num_units);
       WorkItem w;
       while (ok && walk.next(&w)) {
         const int32_t kb_begin = w.kb0, kb_end = w.kb1;
@@ -422,7 +426,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const long long st_begin = clock64();
 #endif
       WorkWalk walk;
-      walk.init(p, unit, num_units);
+      walk.template init<kStreamK>(p, unit, num_units);
       WorkItem w;
       while (ok && walk.next(&w)) {
         const int32_t kb_begin = w.kb0, kb_end = w.kb1;
@@ -515,12 +519,12 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
     // 32 pieces in 32 different rows, and splitk_finish_kernel reads them back the same way.
     float* const split_tile = splitk ? p.split_ws + static_cast<int64_t>(k_slice) * p.num_tiles * (kTileM * bn) : nullptr;
     WorkWalk walk;
-    walk.init(p, unit, num_units);
+    walk.template init<kStreamK>(p, unit, num_units);
     WorkItem w;
     while (walk.next(&w)) {
       const int32_t t = w.tile;
-      const bool sk_later = w.kind == 2;       // raw store, no program, no reductions
-      const bool sk_first = w.kind == 1;       // add the later parts, then the usual epilogue
+      const bool sk_later = kStreamK && w.kind == 2;       // raw store, no program, no reductions
+      const bool sk_first = kStreamK && w.kind == 1;       // add the later parts, then the usual epilogue
       int32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
       const int32_t tm128 = tm * CG + static_cast<int32_t>(cta_rank);   // index of this CTA's 128-row block

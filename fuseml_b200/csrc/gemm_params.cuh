@@ -131,6 +131,9 @@ struct WorkWalk {
   int32_t hp_pos, hp_end, hp_len, hp_own, hp_index;              // a helper's run of left-over K blocks (hp_pos >= hp_end: none)
   int32_t splitk_tile, splitk_kb0, splitk_kb1;                   // split-K item (kind 3), -1 when taken
 
+  // SK = false compiles the K-split last wave out (kernel instances that never run it: their
+  // register budget has no room for the walk's extra state)
+  template <bool SK = true>
   __host__ __device__ void init(const GemmParams& p, int32_t unit_, int32_t units_) {
     unit = unit_; units = units_; num_kb = p.num_kb;
     splitk_tile = -1; splitk_kb0 = splitk_kb1 = 0;
@@ -145,7 +148,7 @@ struct WorkWalk {
       next_dp = 0;
       return;
     }
-    const int32_t rem = p.stream_k ? p.num_tiles % units : 0;
+    const int32_t rem = (SK && p.stream_k) ? p.num_tiles % units : 0;
     const int32_t slices = rem > 0 ? units / rem : 0;       // K slices per last-wave tile
     dp_tiles = p.num_tiles;
     next_dp = unit;

@@ -173,9 +173,13 @@ typedef struct {
  * the workspace is reused and only A is expanded.  The caller vouches that neither B nor that
  * part of the workspace was written in between.                                            */
 #define FUSEML_PLAN_B_EXPANSION_VALID 1
-/* plan.flags bit, set by the router for CTA-pair launches whose last wave holds at most half as
- * many tiles as there are CTA pairs: each of those tiles is cut into equal K slices, one per
- * pair (later slices pass through the workspace and are added in slice order).             */
+/* plan.flags bit: the tiles of a ragged last wave of a CTA-pair launch are shared between all
+ * pairs by K ranges; later parts pass through the workspace and are added in a fixed order
+ * (fuseml_sm100_schedule shows the walk).  The router sets it when the last wave holds at most
+ * half as many tiles as there are CTA pairs (each tile then falls into equal K slices, one per
+ * pair) and the K loop is long.  Needs plan.cluster == 2 and plan.grid = 2 x the pairs that run
+ * at once; ignored for programs that keep a second value register (SAVE / SWAP / *_SAVED left
+ * after the gelu*sigmoid rewrite), which run whole tiles.                                  */
 #define FUSEML_PLAN_STREAM_K 2
 
 typedef struct {
