@@ -261,6 +261,26 @@ def test_k_split_schedule_covers_every_k_block_once(native_lib, M, Nn, K, grid):
     assert sum(len(v) for v in plain.values()) == tiles
 
 
+def test_saved_register_programs_keep_whole_tiles(native_lib):
+    """A program that keeps a second value register runs in a kernel instance without the K-split
+    walk: the flag is ignored and the schedule says so.  The gelu*sigmoid diamond is rewritten to
+    one op first and does not count."""
+    d = _desc(4096, 4096, 16384)
+    rc, p = _plan(native_lib, d)
+    assert rc == N.OK and p.flags & N.PLAN_STREAM_K          # 256 tiles, 34 left, 256 K blocks
+    assert any(w.kind != 0 for items in _schedule(native_lib, d, p).values() for w in items)
+    for i, oc in enumerate((N.OP_SAVE, N.OP_RELU, N.OP_ADD_SAVED)):
+        d.ops[i].opcode = oc
+    d.n_ops = 3
+    sched = _schedule(native_lib, d, p)
+    assert all(w.kind == 0 for items in sched.values() for w in items)
+    assert sum(len(v) for v in sched.values()) == 256
+    for i, oc in enumerate((N.OP_SAVE, N.OP_GELU_ERF, N.OP_SWAP, N.OP_SIGMOID, N.OP_MUL_SAVED)):
+        d.ops[i].opcode = oc
+    d.n_ops = 5
+    assert any(w.kind != 0 for items in _schedule(native_lib, d, p).values() for w in items)
+
+
 def test_schedule_of_a_split_k_plan_and_bad_arguments(native_lib):
     d = _desc(128, 512, 2048)
     rc, p = _plan(native_lib, d)

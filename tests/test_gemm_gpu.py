@@ -738,6 +738,7 @@ STREAM_K_CASES = [
     (2048, 16384, 4096, None, "res", ()),           # 128 tiles: a whole wave, then 54 owners and 20 helpers
     (1280, 448, 256, 16, "gelu", ("sum", "max")),   # 5 tiles on 8 pairs, 7 K blocks: two helpers, one pair idle; reductions
     (200, 2560, 2200, 20, "res", ()),               # 9 tiles on 10 pairs: one helper adds 4 K blocks to every tile; ragged
+    (600, 4096, 1000, 10, "saved", ()),             # a second value register: the flag is ignored, whole tiles
 ]
 
 
@@ -756,7 +757,8 @@ def test_stream_k_matches_whole_tile_waves(K, M, Kd, Nn, grid, epi, red):
 
     def program():
         prog = K.EpilogueProgram().bias(bias)
-        return {"gelu": prog.gelu, "relu": prog.relu, "res": lambda: prog.add_tensor(r)}[epi]()
+        return {"gelu": prog.gelu, "relu": prog.relu, "res": lambda: prog.add_tensor(r),
+                "saved": lambda: prog.save().relu().add_saved()}[epi]()
 
     outs = []
     for on in (True, False):
@@ -781,7 +783,8 @@ def test_stream_k_matches_whole_tile_waves(K, M, Kd, Nn, grid, epi, red):
     else:
         y_on, y_off = on, off
     h = a.double() @ w.double().t() + bias.double()
-    ref = {"gelu": torch.nn.functional.gelu, "relu": torch.relu, "res": lambda t: t + r.double()}[epi](h)
+    ref = {"gelu": torch.nn.functional.gelu, "relu": torch.relu, "res": lambda t: t + r.double(),
+           "saved": lambda t: torch.relu(t) + t}[epi](h)
     np.testing.assert_allclose(y_on.float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
     np.testing.assert_allclose(y_off.float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
     assert not torch.isnan(y_on.float()).any()
