@@ -307,6 +307,49 @@ def test_compiled_forward_replays_from_a_cuda_graph(native_lib):
     torch._dynamo.reset()
 
 
+def test_k_split_last_wave_through_the_compiler_and_a_cuda_graph(native_lib):
+    """A Linear whose tile count leaves a third of a wave (2560 x 2560 outputs = 100 pair tiles on
+    74 pairs, 128 K blocks): the router marks the plan FUSEML_PLAN_STREAM_K, the launcher sizes the
+    workspace for the partial tiles and flags, and the launch (a memset of the flags + the
+    kernel) is captured and replayed like any other."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import fuseml_b200 as F
+    from fuseml_b200 import _native as N
+    from fuseml_b200.runtime import GraphedCallable
+
+    torch._dynamo.reset()
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(8192, 2560).to(device="cuda", dtype=torch.bfloat16)
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = lin
+
+        def forward(self, x):
+            return torch.nn.functional.gelu(self.lin(x))
+
+    comp = F.FuseMLCompiler()
+    compiled = torch.compile(Block(), backend=comp)
+    x = torch.randn(2560, 8192, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        y = compiled(x)
+        plans = [p.plan for L in set(comp.launchers) for p in L._prepared.values()]
+        assert plans and all(p.flags & N.PLAN_STREAM_K and p.cluster == 2 and p.grid == 148 for p in plans)
+        ref = torch.nn.functional.gelu(x.float() @ lin.weight.float().t() + lin.bias.float())
+        np.testing.assert_allclose(y.float().cpu().numpy(), ref.cpu().numpy(), rtol=1.6e-2, atol=1e-2)
+        static_x = x.clone()
+        graphed = GraphedCallable(compiled, static_x)
+        y0 = graphed().clone()
+        static_x.copy_(-x)
+        y1 = graphed().clone()
+        torch.cuda.synchronize()
+        assert F.device_status() == 0
+        assert torch.equal(y0, y) and torch.equal(y1, compiled(-x)) and not torch.equal(y0, y1)
+    torch._dynamo.reset()
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_training_step_runs_fused_forward_and_backward(native_lib, dtype):
     """Forward and backward of the residual MLP block through the compiler.  The forward graph of a
