@@ -40,6 +40,7 @@ OP_NAMES = {
 RED_SUM, RED_MAX, RED_MEAN = 1, 2, 4
 PLAN_B_EXPANSION_VALID = 1
 PLAN_STREAM_K = 2
+PLAN_GROUP_N = 4
 MLP_WEIGHTS_EXPANDED = 1
 WHERE_MMA_FULL = 0x202
 AXIS_M, AXIS_N, AXIS_ALL = 0, 1, 2

@@ -14,7 +14,7 @@ fuseml/codegen/kernel_generator.py:1067-1172) and re-runs Triton's autotuner in 
 launch it is building towards); here the tuned result itself is what is stored.
 
 File format: ``{"version": 1, "plans": {key: {"tile_n", "cluster", "grid", "group_m",
-"split_k", "stream_k", "us", "candidates"}}}``.  The key names the device, the library build, the problem
+"split_k", "stream_k", "group_n", "us", "candidates"}}}``.  The key names the device, the library build, the problem
 (M, N, K, dtypes, B layout) and the epilogue signature, so a rebuilt library or another GPU
 never picks up a stale entry.  Writes are atomic (temp file + rename).
 """
@@ -112,14 +112,17 @@ def apply_entry(plan: N.Plan, entry: dict) -> bool:
         return False
     for k, v in vals.items():
         setattr(plan, k, v)
-    if "stream_k" in entry:            # absent in entries written before the flag existed: the router's choice stands
-        plan.flags = (plan.flags & ~N.PLAN_STREAM_K) | (N.PLAN_STREAM_K if entry["stream_k"] else 0)
+    # flag entries are absent in files written before the flag existed: the router's choice stands
+    for name, bit in (("stream_k", N.PLAN_STREAM_K), ("group_n", N.PLAN_GROUP_N)):
+        if name in entry:
+            plan.flags = (plan.flags & ~bit) | (bit if entry[name] else 0)
     return True
 
 
 def entry_of(plan: N.Plan, us: float | None = None, candidates: int = 0) -> dict:
     e = {k: int(getattr(plan, k)) for k in _FIELDS}
     e["stream_k"] = int(bool(plan.flags & N.PLAN_STREAM_K))
+    e["group_n"] = int(bool(plan.flags & N.PLAN_GROUP_N))
     if us is not None:
         e["us"] = round(float(us), 3)
     e["candidates"] = int(candidates)
@@ -146,7 +149,8 @@ def candidate_plans(base: N.Plan, M: int, Ncols: int, sm_count: int = 148, has_r
             tiles = tiles_m * -(-Ncols // bn)
             if -(-tiles // units) * bn < base_waves:          # fewer column-waves of work
                 add(tile_n=bn, grid=min(tiles, units) * 2)
-        for gm in (max(1, base.group_m // 2), min(tiles_m, base.group_m * 2)):
+        along = -(-Ncols // base.tile_n) if base.flags & N.PLAN_GROUP_N else tiles_m     # what group_m counts
+        for gm in (max(1, base.group_m // 2), min(along, base.group_m * 2)):
             add(group_m=gm)
         rem = (tiles_m * -(-Ncols // base.tile_n)) % units
         if 0 < rem and not has_reduction:                     # the last wave shared by K ranges, or not

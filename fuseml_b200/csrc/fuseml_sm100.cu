@@ -231,7 +231,7 @@ static int check_plan(const fuseml_plan_t* pl) {
   if (pl->grid <= 0 || pl->group_m <= 0) return FUSEML_E_PLAN;
   if (pl->cluster != 1 && pl->cluster != 2) return FUSEML_E_PLAN;
   if (pl->cluster == 2 && pl->tile_n <= 128) return FUSEML_E_PLAN;
-  if (pl->split_k < 0 || pl->split_k > 64 || (pl->flags & ~(FUSEML_PLAN_B_EXPANSION_VALID | FUSEML_PLAN_STREAM_K)) != 0)
+  if (pl->split_k < 0 || pl->split_k > 64 || (pl->flags & ~(FUSEML_PLAN_B_EXPANSION_VALID | FUSEML_PLAN_STREAM_K | FUSEML_PLAN_GROUP_N)) != 0)
     return FUSEML_E_PLAN;
   if ((pl->flags & FUSEML_PLAN_STREAM_K) && (pl->cluster != 2 || pl->split_k > 1)) return FUSEML_E_PLAN;
   if (pl->split_k > 1 && pl->cluster != 1) return FUSEML_E_PLAN;
@@ -395,7 +395,7 @@ int fuseml_sm100_gemm_epilogue(const fuseml_gemm_desc_t* desc, const fuseml_plan
   p.tiles_n = static_cast<int32_t>((desc->N + BN - 1) / BN);
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.bn = BN;
-  p.group_m = std::min(plan.group_m, p.tiles_m);
+  p.group_m = (plan.flags & FUSEML_PLAN_GROUP_N) ? -std::min(plan.group_m, p.tiles_n) : std::min(plan.group_m, p.tiles_m);
   p.num_kb = static_cast<int32_t>((K + BK - 1) / BK);
   p.d = desc->d;
   p.ldd = desc->ldd;

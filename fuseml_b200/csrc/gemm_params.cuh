@@ -89,8 +89,21 @@ struct GemmParams {
 // of B columns and a short stack of A row blocks, which keeps both resident in
 // L2 (same idea as the GROUP_SIZE_M swizzle of the reference,
 // fuseml/codegen/kernel_generator.py:1278-1286).
+// group_m < 0 (FUSEML_PLAN_GROUP_N): bands of -group_m tile columns instead, columns fastest
+// inside a band, all rows of one band before the next band.
 __host__ __device__ inline void tile_coords(int32_t t, int32_t tiles_m, int32_t tiles_n, int32_t group_m,
                                             int32_t* tm, int32_t* tn) {
+  if (group_m < 0) {
+    const int32_t g = -group_m;
+    const int32_t band_size = g * tiles_m;
+    const int32_t band = t / band_size;
+    const int32_t first_n = band * g;
+    const int32_t cols = (tiles_n - first_n) < g ? (tiles_n - first_n) : g;
+    const int32_t r = t - band * band_size;
+    *tn = first_n + (r % cols);
+    *tm = r / cols;
+    return;
+  }
   const int32_t group_size = group_m * tiles_n;
   const int32_t group_id = t / group_size;
   const int32_t first_m = group_id * group_m;

@@ -295,8 +295,23 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
     int64_t gw = 1;
     while (gw * 2 <= tiles_m && static_cast<double>(gw * 2) * static_cast<double>(gw * 2) * slab_per_tile_row <=
                                     static_cast<double>(units) * slab_per_tile_col) gw *= 2;
-    if (gm < gw && tiles >= 2 * units) gm = gw;
-    plan->group_m = static_cast<int32_t>(std::max<int64_t>(1, std::min<int64_t>(gm, tiles_m)));
+    if (gm < gw && tiles >= 2 * units) {
+      gm = gw;
+      // Waves do not end where groups end: a wave that straddles two groups of gw rows x all
+      // columns reads the row slabs of both.  The longer the groups the rarer that is, so with
+      // more tile rows than tile columns the groups run the other way, bands of columns through
+      // all the rows (FUSEML_PLAN_GROUP_N), sized by the same square-wave rule.
+      if (tiles_m > tiles_n) {
+        int64_t gn = 1;
+        while (gn * 2 <= tiles_n && static_cast<double>(gn * 2) * static_cast<double>(gn * 2) * slab_per_tile_col <=
+                                        static_cast<double>(units) * slab_per_tile_row) gn *= 2;
+        if (gn * tiles_m > gw * tiles_n) {
+          gm = gn;
+          plan->flags |= FUSEML_PLAN_GROUP_N;
+        }
+      }
+    }
+    plan->group_m = static_cast<int32_t>(std::max<int64_t>(1, std::min<int64_t>(gm, (plan->flags & FUSEML_PLAN_GROUP_N) ? tiles_n : tiles_m)));
   }
 
   // Shared memory: ring of (A 16 KB + this CTA's share of B) stages under the opt-in budget.

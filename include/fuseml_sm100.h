@@ -181,6 +181,12 @@ typedef struct {
  * at once; ignored for programs that keep a second value register (SAVE / SWAP / *_SAVED left
  * after the gelu*sigmoid rewrite), which run whole tiles.                                  */
 #define FUSEML_PLAN_STREAM_K 2
+/* plan.flags bit: group_m counts tile columns, not tile rows: tiles are walked in bands of group_m
+ * tile columns (columns fastest inside a band, all tile rows of a band before the next band).
+ * The router sets it for long K loops when there are more tile rows than tile columns: a wave
+ * of concurrently running tiles is then a compact block of about group_m columns whatever its
+ * position, and reads the fewest operand slabs.                                             */
+#define FUSEML_PLAN_GROUP_N 4
 
 typedef struct {
   int32_t tile_m;        /* 128                                              */

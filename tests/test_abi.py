@@ -122,6 +122,18 @@ def test_plan_budgets_and_bounds(native_lib):
     assert rc == N.OK and (p.tile_n, p.split_k, p.grid) == (32, 1, 16)
 
 
+def test_plan_rasterisation_groups(native_lib):
+    """Groups of tile rows whose A slab stays within 32 MiB; with a long K loop (slabs of 8.4 MB
+    per tile row) square waves instead, as bands of columns when there are more tile rows than
+    tile columns."""
+    for (M, Nn, K), gm, band in (((8192, 16384, 4096), 16, False), ((8192, 4096, 4096), 16, False),
+                                 ((8192, 4096, 16384), 8, True), ((32768, 4096, 16384), 8, True),
+                                 ((4096, 4096, 16384), 8, False), ((8192, 8192, 8192), 8, False),
+                                 ((2048, 4096, 16384), 4, False)):
+        rc, p = _plan(native_lib, _desc(M, Nn, K))
+        assert rc == N.OK and p.group_m == gm and bool(p.flags & N.PLAN_GROUP_N) == band, (M, Nn, K, p.group_m, p.flags)
+
+
 def test_plan_follows_device_props(native_lib):
     props = N.DeviceProps()
     native_lib.fuseml_sm100_query(C.byref(props))   # fills B200 defaults when there is no device
@@ -172,7 +184,7 @@ def test_a_zeroed_or_garbage_plan_is_a_status_code_not_a_crash(native_lib):
     rc, good = _plan(native_lib, d)
     assert rc == N.OK
     for field, value in (("tile_n", 0), ("tile_n", 48), ("tile_m", 64), ("grid", 0), ("group_m", 0), ("cluster", 3),
-                         ("split_k", 65), ("flags", 4)):
+                         ("split_k", 65), ("flags", 8)):
         bad = N.Plan.from_buffer_copy(good)
         setattr(bad, field, value)
         assert native_lib.fuseml_sm100_workspace_bytes(C.byref(d), C.byref(bad)) == -1, field

@@ -726,6 +726,47 @@ def test_small_mlp_block_declines_what_it_cannot_run(K):
 
 # ---- K-split last wave ---------------------------------------------------------
 
+@pytest.mark.parametrize("M,Kd,Nn,group,red", [
+    (1500, 512, 2300, 3, ()),              # 6 x 9 pair tiles, bands of 3 columns, ragged edges
+    (1500, 512, 2300, 4, ("sum", "max")),  # a last band of one column; row reductions
+    (700, 1024, 1300, 8, ()),              # a band wider than the matrix: one band
+    (2048, 8192, 4096, 2, ()),             # 8 x 16 tiles in eight bands: several tiles per pair
+])
+def test_column_band_rasterisation_matches_row_groups(K, M, Kd, Nn, group, red):
+    """FUSEML_PLAN_GROUP_N only changes the order in which tiles are visited: every tile is still
+    computed exactly once, so outputs (and reductions, up to the order of their partial sums) equal
+    those of the row-group walk bit for bit."""
+    from fuseml_b200 import _native as N
+
+    g = torch.Generator().manual_seed(M + Nn + group)
+    a = torch.randn(M, Kd, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(Nn, Kd, generator=g) / Kd ** 0.5).to(torch.bfloat16).cuda()
+    bias = torch.randn(Nn, generator=g).to(torch.bfloat16).cuda()
+    outs = []
+    for band in (True, False):
+        out = torch.full((M, Nn), float("nan"), dtype=torch.bfloat16, device="cuda")
+        prog = K.EpilogueProgram().bias(bias).gelu()
+        desc = N.GemmDesc()
+        K.fill_desc(desc, a, w.t(), prog, out, torch.bfloat16)
+        plan = K.plan_for(desc, K.device_props())
+        plan.group_m = group
+        plan.flags = (plan.flags | N.PLAN_GROUP_N) if band else (plan.flags & ~N.PLAN_GROUP_N)
+        res = K.fused_gemm(a, w.t(), K.EpilogueProgram().bias(bias).gelu(), out=out, plan=plan, reduce=red,
+                           axis=-1 if red else None)
+        torch.cuda.synchronize()
+        _status_ok(K)
+        outs.append(res)
+    if red:
+        (y_band, r_band), (y_rows, r_rows) = outs
+        for k in red:
+            assert torch.equal(r_band[k], r_rows[k]), k      # per-row partials are indexed by tile column, not by visit order
+    else:
+        y_band, y_rows = outs
+    assert not torch.isnan(y_band.float()).any() and torch.equal(y_band, y_rows)
+    ref = torch.nn.functional.gelu(a.double() @ w.double().t() + bias.double())
+    np.testing.assert_allclose(y_band.float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
+
+
 STREAM_K_CASES = [
     # M, K, N, grid (CTAs; None = the router's), epilogue, reductions
     (1024, 4096, 16384, None, "gelu", ()),          # 256 tiles on 74 pairs: 3 whole waves + 34 tiles in two K slices each
