@@ -281,37 +281,33 @@ int make_plan(const fuseml_gemm_desc_t* d, const fuseml_device_props_t* props_in
   // depend on group_m, but the saved DRAM traffic returns as SM clock (8192 x 16384 x 4096:
   // group of 16 against 4, 3.7x less DRAM traffic, 8 % faster); slabs above a quarter of L2
   // lose again.  So: the largest power of two whose slab stays within 32 MiB.
-  // With a long K even a few tile rows exceed that and nothing is kept from wave to wave; what
-  // counts then is what one wave of `units` tiles reads, group_m row slabs plus units / group_m
-  // column slabs, least for a square wave: group_m is raised to the power of two below
-  // sqrt(units * column slab / row slab).  Measured (8192 x 4096 x 16384, 8.4 MB per slab, one
-  // launch under ncu): groups of 4 tile rows read 2.1 GB in 789 us, groups of 8 1.77 GB in 770 us,
-  // groups of 2 1.88 GB, groups of 16 more again.
+  // With more tile rows than tile columns the same is done the other way round
+  // (FUSEML_PLAN_GROUP_N): bands of group_m tile columns walked through all the tile rows, the
+  // band's columns of B kept while A streams past once per band.  The groups are then longer
+  // (more waves per group, fewer waves that straddle two groups and read the kept slabs of
+  // both): 8192 x 4096 x 4096 with row reductions 214 -> 210 us, 16384 x 4096 x 8192 885 -> 871 us,
+  // both held under the power cap.
+  // With a long K even a few slabs exceed the bound and nothing is kept from wave to wave; what
+  // counts then is what one wave of `units` tiles reads, g slabs of the kept operand plus
+  // units / g of the other, least for a square wave: g is raised to the power of two below
+  // sqrt(units * other slab / kept slab).  Measured (8192 x 4096 x 16384, 8.4 MB per slab, one
+  // launch under ncu): groups of 4 tile rows read 2.1 GB in 789 us, groups of 8 tile rows 1.77 GB
+  // in 770 us, bands of 8 tile columns 1.34 GB; the four-block stack of such GEMMs runs 3.4 %
+  // faster under the power cap with the bands than with groups of 4 rows.
   {
     const double slab_per_tile_row = 128.0 * cg * static_cast<double>(k_pad) * (f32 ? 4 : eb);
     const double slab_per_tile_col = static_cast<double>(best_bn) * static_cast<double>(k_pad) * (f32 ? 4 : eb);
-    int64_t gm = 1;
-    while (gm * 2 <= tiles_m && static_cast<double>(gm * 2) * slab_per_tile_row <= 32.0 * 1024 * 1024) gm *= 2;
+    const bool by_cols = tiles_m > tiles_n && tiles >= 2 * units;
+    const double kept = by_cols ? slab_per_tile_col : slab_per_tile_row;
+    const double other = by_cols ? slab_per_tile_row : slab_per_tile_col;
+    const int64_t along = by_cols ? tiles_n : tiles_m;
+    int64_t g = 1;
+    while (g * 2 <= along && static_cast<double>(g * 2) * kept <= 32.0 * 1024 * 1024) g *= 2;
     int64_t gw = 1;
-    while (gw * 2 <= tiles_m && static_cast<double>(gw * 2) * static_cast<double>(gw * 2) * slab_per_tile_row <=
-                                    static_cast<double>(units) * slab_per_tile_col) gw *= 2;
-    if (gm < gw && tiles >= 2 * units) {
-      gm = gw;
-      // Waves do not end where groups end: a wave that straddles two groups of gw rows x all
-      // columns reads the row slabs of both.  The longer the groups the rarer that is, so with
-      // more tile rows than tile columns the groups run the other way, bands of columns through
-      // all the rows (FUSEML_PLAN_GROUP_N), sized by the same square-wave rule.
-      if (tiles_m > tiles_n) {
-        int64_t gn = 1;
-        while (gn * 2 <= tiles_n && static_cast<double>(gn * 2) * static_cast<double>(gn * 2) * slab_per_tile_col <=
-                                        static_cast<double>(units) * slab_per_tile_row) gn *= 2;
-        if (gn * tiles_m > gw * tiles_n) {
-          gm = gn;
-          plan->flags |= FUSEML_PLAN_GROUP_N;
-        }
-      }
-    }
-    plan->group_m = static_cast<int32_t>(std::max<int64_t>(1, std::min<int64_t>(gm, (plan->flags & FUSEML_PLAN_GROUP_N) ? tiles_n : tiles_m)));
+    while (gw * 2 <= along && static_cast<double>(gw * 2) * static_cast<double>(gw * 2) * kept <= static_cast<double>(units) * other) gw *= 2;
+    if (g < gw && tiles >= 2 * units) g = gw;
+    if (by_cols) plan->flags |= FUSEML_PLAN_GROUP_N;
+    plan->group_m = static_cast<int32_t>(std::max<int64_t>(1, std::min<int64_t>(g, along)));
   }
 
   // Shared memory: ring of (A 16 KB + this CTA's share of B) stages under the opt-in budget.

@@ -123,10 +123,11 @@ def test_plan_budgets_and_bounds(native_lib):
 
 
 def test_plan_rasterisation_groups(native_lib):
-    """Groups of tile rows whose A slab stays within 32 MiB; with a long K loop (slabs of 8.4 MB
-    per tile row) square waves instead, as bands of columns when there are more tile rows than
-    tile columns."""
-    for (M, Nn, K), gm, band in (((8192, 16384, 4096), 16, False), ((8192, 4096, 4096), 16, False),
+    """Groups of tile rows whose A slab stays within 32 MiB, or, with more tile rows than tile
+    columns, bands of tile columns whose B slab does; with a long K loop (slabs of 8.4 MB)
+    square waves instead."""
+    for (M, Nn, K), gm, band in (((8192, 16384, 4096), 16, False), ((8192, 4096, 4096), 16, True),
+                                 ((16384, 4096, 8192), 8, True), ((256, 16384, 4096), 1, False),
                                  ((8192, 4096, 16384), 8, True), ((32768, 4096, 16384), 8, True),
                                  ((4096, 4096, 16384), 8, False), ((8192, 8192, 8192), 8, False),
                                  ((2048, 4096, 16384), 4, False)):
