@@ -49,7 +49,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # mean of its two launches (first GEMM 0.669 GB, second GEMM 1.337 GB: with K = 16384 the operand
 # slabs of one wave of tiles do not survive in L2 until the next wave; algorithmic bytes are
 # 0.47 GB per launch).  cfg5 was not captured (the same two kernels as cfg4, four times).
-NCU_TRAFFIC_BYTES = {"cfg1": None, "cfg4": 1.0033e9, "cfg2": 1.483e8, "cfg3": 1.504e8, "cfg5": None,
+NCU_TRAFFIC_BYTES = {"cfg1": None, "cfg4": 1.0033e9, "cfg2": 1.483e8, "cfg3": 1.065e8, "cfg5": None,
                      "cfg4_training_step": None}
 
 
