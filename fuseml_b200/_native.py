@@ -108,7 +108,7 @@ class Plan(C.Structure):
 class WorkItem(C.Structure):
     """``fuseml_work_item_t``: one entry of a unit's schedule (``fuseml_sm100_schedule``)."""
     _fields_ = [("tile", C.c_int32), ("kb0", C.c_int32), ("kb1", C.c_int32), ("kind", C.c_int32),
-                ("after", C.c_int32), ("slot", C.c_int32)]
+                ("after", C.c_int32), ("slot", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32)]
 
 
 class DeviceProps(C.Structure):

@@ -884,6 +884,7 @@ int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_
   p.tiles_n = static_cast<int32_t>((desc->N + plan_in->tile_n - 1) / plan_in->tile_n);
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.num_kb = static_cast<int32_t>((K + BK - 1) / BK);
+  p.group_m = (plan_in->flags & FUSEML_PLAN_GROUP_N) ? -std::min(plan_in->group_m, p.tiles_n) : std::min(plan_in->group_m, p.tiles_m);
   int32_t units;
   if (plan_in->split_k > 1) {
     p.kb_per_split = (p.num_kb + plan_in->split_k - 1) / plan_in->split_k;
@@ -902,7 +903,11 @@ int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_
   WorkItem w;
   int32_t n = 0;
   while (walk.next(&w)) {
-    if (n < max_items) items[n] = fuseml_work_item_t{w.tile, w.kb0, w.kb1, w.kind, w.after, w.slot};
+    if (n < max_items) {
+      int32_t tm, tn;
+      tile_coords(w.tile, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
+      items[n] = fuseml_work_item_t{w.tile, w.kb0, w.kb1, w.kind, w.after, w.slot, tm, tn};
+    }
     ++n;
   }
   return n;

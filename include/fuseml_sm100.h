@@ -339,6 +339,8 @@ typedef struct {
                           parts from workspace slots slot..slot+after-1; 2 later part, stored to
                           workspace slot `slot`; 3 split-K slice                                   */
   int32_t after, slot;
+  int32_t tile_m, tile_n; /* the tile's row and column in units of tiles (plan.group_m and
+                             FUSEML_PLAN_GROUP_N decide how `tile` maps onto them)                */
 } fuseml_work_item_t;
 int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_t* plan, int32_t unit,
                               fuseml_work_item_t* items, int32_t max_items, int32_t* n_units);

@@ -274,6 +274,35 @@ def test_k_split_schedule_covers_every_k_block_once(native_lib, M, Nn, K, grid):
     assert sum(len(v) for v in plain.values()) == tiles
 
 
+@pytest.mark.parametrize("M,Nn,band,group", [(1500, 2300, False, 4), (1500, 2300, True, 4), (1500, 2300, True, 3),
+                                             (8192, 4096, True, 8), (8192, 4096, False, 16), (700, 5000, True, 64),
+                                             (5000, 700, False, 64), (300, 300, True, 1)])
+def test_rasterisation_visits_every_tile_position_once(native_lib, M, Nn, band, group):
+    """Tile index -> (tile row, tile column) is a bijection in both walks (groups of tile rows,
+    bands of tile columns), ragged last group or band included, and consecutive tiles stay inside
+    one group or band until it is exhausted."""
+    d = _desc(M, Nn, 4096)
+    rc, p = _plan(native_lib, d)
+    assert rc == N.OK
+    p.group_m = group
+    p.flags = (p.flags | N.PLAN_GROUP_N) if band else (p.flags & ~N.PLAN_GROUP_N)
+    p.flags &= ~N.PLAN_STREAM_K
+    rows = -(-M // (128 * p.cluster))
+    cols = -(-Nn // p.tile_n)
+    p.grid = p.cluster * min(rows * cols, 74 if p.cluster == 2 else 148)
+    sched = _schedule(native_lib, d, p)
+    by_tile = {w.tile: (w.tile_m, w.tile_n) for items in sched.values() for w in items}
+    assert sorted(by_tile) == list(range(rows * cols))
+    assert sorted(by_tile.values()) == [(r, c) for r in range(rows) for c in range(cols)]
+    order = [by_tile[t] for t in range(rows * cols)]
+    keys = [(c // group) if band else (r // group) for r, c in order]
+    assert keys == sorted(keys)                       # one group / band after the other
+    first = [rc_ for rc_, k in zip(order, keys) if k == 0]
+    inner = [c for _, c in first] if band else [r for r, _ in first]
+    width = min(group, cols if band else rows)
+    assert inner[:width] == list(range(width))        # the grouped index runs fastest
+
+
 def test_saved_register_programs_keep_whole_tiles(native_lib):
     """A program that keeps a second value register runs in a kernel instance without the K-split
     walk: the flag is ignored and the schedule says so.  The gelu*sigmoid diamond is rewritten to
