@@ -117,11 +117,23 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const C
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[2];
   int n_attr = 0;
-  // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the
-  // stream drains; it waits (griddepcontrol.wait) before its first global access.
-  attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
-  ++n_attr;
+  // K-split last wave: CTA pairs wait for other pairs of the same launch, so all of them have to
+  // be resident at once.  Alone on the device they are (the grid is clamped to what the device
+  // holds), but next to another persistent kernel on another stream each could hold SMs the other
+  // is waiting for.  A cooperative launch starts only when the whole grid fits, which rules that
+  // out; it replaces the programmatic dependent launch for these (long) kernels.
+  const bool cooperative = CG == 2 && p.stream_k != 0;
+  if (cooperative) {
+    attr[n_attr].id = cudaLaunchAttributeCooperative;
+    attr[n_attr].val.cooperative = 1;
+    ++n_attr;
+  } else {
+    // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the
+    // stream drains; it waits (griddepcontrol.wait) before its first global access.
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
   if (CG == 2) {
     int pairs = grid / 2;
     if (max_clusters > 0 && pairs > max_clusters) pairs = max_clusters;
@@ -136,7 +148,15 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const C
   cfg.blockDim = dim3(v2::threads_for(EW));
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tr, td, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tr, td, p);
+  if (e != cudaSuccess && cooperative) {
+    // a driver that refuses the combination: launch as the other kernels are (the bounded waits
+    // of the kernel still turn a missing partner into a status code, never into a hang)
+    cudaGetLastError();
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tr, td, p);
+  }
   if (e != cudaSuccess) { cudaGetLastError(); return FUSEML_E_LAUNCH; }
   return FUSEML_OK;
 }

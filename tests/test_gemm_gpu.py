@@ -767,6 +767,42 @@ def test_column_band_rasterisation_matches_row_groups(K, M, Kd, Nn, group, red):
     np.testing.assert_allclose(y_band.float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
 
 
+def test_k_split_launches_on_two_streams_do_not_wait_for_each_other(K):
+    """In a K-split launch CTA pairs wait for other pairs of the same launch, so the whole grid has
+    to be resident at once; such a kernel is launched cooperatively, which keeps two of them on two
+    streams from each holding SMs the other needs.  Ten rounds of two concurrent launches finish
+    with a clean status word and the right values."""
+    from fuseml_b200 import _native as N
+
+    M, Nn, Kd = 2560, 2560, 8192              # 100 pair tiles on 74 pairs: 26 left, two K slices each
+    g = torch.Generator().manual_seed(11)
+    sets = []
+    for _ in range(2):
+        a = torch.randn(M, Kd, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(Nn, Kd, generator=g) / Kd ** 0.5).to(torch.bfloat16).cuda()
+        r = torch.randn(M, Nn, generator=g).to(torch.bfloat16).cuda()
+        sets.append((a, w, r, torch.empty(M, Nn, dtype=torch.bfloat16, device="cuda")))
+    desc = N.GemmDesc()
+    K.fill_desc(desc, sets[0][0], sets[0][1].t(), K.EpilogueProgram().add_tensor(sets[0][2]), sets[0][3], torch.bfloat16)
+    plan = K.plan_for(desc, K.device_props())
+    assert plan.flags & N.PLAN_STREAM_K and plan.grid == 148
+    K.set_diagnostics(wait_limit_us=200_000)   # a wait that ran out would show within 0.2 s, as a status code
+    try:
+        streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+        torch.cuda.synchronize()
+        for _ in range(10):
+            for st, (a, w, r, out) in zip(streams, sets):
+                with torch.cuda.stream(st):
+                    K.fused_gemm(a, w.t(), K.EpilogueProgram().add_tensor(r), out=out, plan=plan)
+        torch.cuda.synchronize()
+        _status_ok(K)
+    finally:
+        K.set_diagnostics()
+    for a, w, r, out in sets:
+        ref = a.double() @ w.double().t() + r.double()
+        np.testing.assert_allclose(out.float().cpu().numpy(), ref.cpu().numpy(), **BF16_TOL)
+
+
 STREAM_K_CASES = [
     # M, K, N, grid (CTAs; None = the router's), epilogue, reductions
     (1024, 4096, 16384, None, "gelu", ()),          # 256 tiles on 74 pairs: 3 whole waves + 34 tiles in two K slices each
