@@ -152,6 +152,10 @@ def candidate_plans(base: N.Plan, M: int, Ncols: int, sm_count: int = 148, has_r
         along = -(-Ncols // base.tile_n) if base.flags & N.PLAN_GROUP_N else tiles_m     # what group_m counts
         for gm in (max(1, base.group_m // 2), min(along, base.group_m * 2)):
             add(group_m=gm)
+        tiles_n = -(-Ncols // base.tile_n)
+        if tiles_m * tiles_n >= 2 * units:                    # the other walk: bands of columns <-> groups of rows
+            other = tiles_m if base.flags & N.PLAN_GROUP_N else tiles_n
+            add(flags=base.flags ^ N.PLAN_GROUP_N, group_m=max(1, min(other, base.group_m)))
         rem = (tiles_m * -(-Ncols // base.tile_n)) % units
         if 0 < rem and not has_reduction:                     # the last wave shared by K ranges, or not
             if base.flags & N.PLAN_STREAM_K:

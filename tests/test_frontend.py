@@ -311,7 +311,8 @@ def test_plan_cache_round_trip_and_candidates(tmp_path):
     # 8192 rows: 27.7 waves, nothing to gain from narrower tiles; the group size varies, and the
     # ragged last wave (50 tiles) may be shared by K ranges
     full = pc.candidate_plans(base, 8192, 16384)
-    assert {c.tile_n for c in full} == {256} and len(full) == 4
+    assert {c.tile_n for c in full} == {256} and len(full) == 5
+    assert sum(1 for c in full if c.flags & N.PLAN_GROUP_N) == 1          # the walk the other way round is tried too
     assert [c.grid for c in full if c.flags & N.PLAN_STREAM_K] == [148]
 
 
