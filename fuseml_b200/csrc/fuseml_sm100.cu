@@ -121,7 +121,8 @@ static int launch_instance(const CUtensorMap& ta, const CUtensorMap& tb, const C
   // be resident at once.  Alone on the device they are (the grid is clamped to what the device
   // holds), but next to another persistent kernel on another stream each could hold SMs the other
   // is waiting for.  A cooperative launch starts only when the whole grid fits, which rules that
-  // out; it replaces the programmatic dependent launch for these (long) kernels.
+  // out; it replaces the programmatic dependent launch for these (long) kernels (both attributes
+  // together are accepted and measure the same).
   const bool cooperative = CG == 2 && p.stream_k != 0;
   if (cooperative) {
     attr[n_attr].id = cudaLaunchAttributeCooperative;
@@ -904,6 +905,7 @@ int32_t fuseml_sm100_schedule(const fuseml_gemm_desc_t* desc, const fuseml_plan_
   p.tiles_n = static_cast<int32_t>((desc->N + plan_in->tile_n - 1) / plan_in->tile_n);
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.num_kb = static_cast<int32_t>((K + BK - 1) / BK);
+  p.red_kinds = desc->reduce.kinds;
   p.group_m = (plan_in->flags & FUSEML_PLAN_GROUP_N) ? -std::min(plan_in->group_m, p.tiles_n) : std::min(plan_in->group_m, p.tiles_m);
   int32_t units;
   if (plan_in->split_k > 1) {

@@ -525,6 +525,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
       const int32_t t = w.tile;
       const bool sk_later = kStreamK && w.kind == 2;       // raw store, no program, no reductions
       const bool sk_first = kStreamK && w.kind == 1;       // add the later parts, then the usual epilogue
+      // exchange: raw store of the half this unit does not finish (pass 0), then the partner's part
+      // is added to the other half and the epilogue runs on it (pass 1)
+      const bool sk_xchg = kStreamK && w.kind == 4;
+      const int32_t left_chunks = (bn / CH + 1) / 2;
+      const bool right_side = w.kb0 != 0;
       int32_t tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, &tm, &tn);
       const int32_t tm128 = tm * CG + static_cast<int32_t>(cta_rank);   // index of this CTA's 128-row block
@@ -568,16 +573,16 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           !ptx::mbar_wait(tile_in_bar, 0u, abort_flag, p.status, kWhereEpilogueTileIn, true)) {
         ok = false;
       }
-      if (sk_first && ok) {
+      // bounded wait for `count` parts in consecutive workspace slots (normally complete by now:
+      // their K ranges are no longer than this unit's)
+      auto wait_parts = [&](int32_t first_slot, int32_t count) {
 #ifdef FUSEML_STALL_COUNTERS
         const long long flag_t0 = clock64();
 #endif
-        // the later parts of this tile lie in `after` consecutive workspace slots, normally
-        // complete by now (their K ranges are no longer than this one); bounded wait on the flags
-        for (int32_t j = 0; j < w.after && ok; ++j) {
-          const volatile uint32_t* flag = p.sk_flags + (static_cast<int64_t>(w.slot + j) * CG + cta_rank);
+        for (int32_t j = 0; j < count && ok; ++j) {
+          const uint32_t* flag = p.sk_flags + (static_cast<int64_t>(first_slot + j) * CG + cta_rank);
           const uint64_t t0 = ptx::globaltimer_ns();
-          while (*flag == 0u) {
+          while (ptx::ld_acquire_gpu(flag) == 0u) {
             __nanosleep(64);
             const uint32_t limit_us = abort_flag[1];
             if (*abort_flag || ptx::globaltimer_ns() - t0 > (limit_us ? static_cast<uint64_t>(limit_us) * 1000ull : ptx::kWaitLimitNs)) {
@@ -587,16 +592,38 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
             }
           }
         }
-        __threadfence();
 #ifdef FUSEML_STALL_COUNTERS
         st_tail += clock64() - flag_t0;
 #endif
+      };
+      // publish the raw part in slot `slot`: the barrier orders every epilogue thread's stores
+      // before thread 64's fence, and the fence (cumulative) orders them before the flag for
+      // whoever reads the flag and fences in turn.  One fence per CTA: a fence per thread waits
+      // for the thread's own stores under a saturated memory system, 256 times over.
+      auto publish_part = [&](int32_t slot) {
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+        if (threadIdx.x == 64 && ok) {
+          __threadfence();
+          *reinterpret_cast<volatile uint32_t*>(p.sk_flags + (static_cast<int64_t>(slot) * CG + cta_rank)) = 1u;
+        }
+      };
+      if (sk_first && ok) wait_parts(w.slot, w.after);
+      const int32_t part_slot0 = sk_xchg ? w.after : w.slot;
+      const int32_t part_count = sk_xchg ? 1 : w.after;
+#pragma unroll 1
+      for (int pass = 0; pass < (sk_xchg ? 2 : 1); ++pass) {
+      if (sk_xchg && pass == 1) {
+        publish_part(w.slot);
+        if (ok) wait_parts(w.after, 1);
       }
+      const bool raw_store = sk_later || (sk_xchg && pass == 0);
+      const bool add_parts = sk_first || (sk_xchg && pass == 1);
 #pragma unroll 1
       for (int c = half; (ok || staged_io) && c < bn / CH; c += kEpiSplit) {
         const int32_t n0 = n_tile0 + c * CH;
         const bool active = ok && n0 < p.N;   // uniform across the warp
         if (!active && !staged_io) break;
+        if (sk_xchg && (((c >= left_chunks) == right_side) != (pass == 1))) continue;   // the other pass's half
         // this thread's 16 columns inside the swizzled 128 x 64 box (box = chunk / 4)
         uint8_t* piece = smem + (c >> 2) * kBoxBytes + (quarter * 32 + lane) * kSwizzleBytes +
                          ((((c & 3) * 2) ^ (lane & 7)) << 4);
@@ -625,10 +652,10 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #ifdef FUSEML_STALL_COUNTERS
           const long long c1 = clock64();
 #endif
-          if (sk_first) {
+          if (add_parts) {
             // later parts in slot order: the sum does not depend on which unit finished first
-            for (int32_t j = 0; j < w.after; ++j) {
-              const float4* src = reinterpret_cast<const float4*>(p.sk_ws + (static_cast<int64_t>(w.slot + j) * CG + cta_rank) * (kTileM * BN)) +
+            for (int32_t j = 0; j < part_count; ++j) {
+              const float4* src = reinterpret_cast<const float4*>(p.sk_ws + (static_cast<int64_t>(part_slot0 + j) * CG + cta_rank) * (kTileM * BN)) +
                                   static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
               float4 x[CH / 4];
 #pragma unroll
@@ -642,11 +669,11 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
               }
             }
           }
-          if (!sk_later) epi::run_program<PROG, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
+          if (!raw_store) epi::run_program<PROG, CH>(p, m, n0, row_ok, v, staged + c * CH, BN, tile_in ? piece : nullptr);
 #ifdef FUSEML_STALL_COUNTERS
           const long long c2 = clock64();
 #endif
-          if (sk_later) {
+          if (raw_store) {
             float4* dst = reinterpret_cast<float4*>(p.sk_ws + (static_cast<int64_t>(w.slot) * CG + cta_rank) * (kTileM * BN)) +
                           static_cast<int64_t>(c) * (CH / 4) * kTileM + (quarter * 32 + lane);
 #pragma unroll
@@ -668,7 +695,7 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           st_prog += c2 - c1;
           st_store += clock64() - c2;
 #endif
-          if (red_any && !sk_later) {
+          if (red_any && !raw_store) {
             if (p.red_axis == FUSEML_AXIS_M) {
               // column reductions transpose 32 x 32 blocks in registers: 32-column chunks only (the
               // host never picks the 16-warp instance for them)
@@ -716,17 +743,8 @@ gemm_epilogue_kernel_v2(const __grid_constant__ CUtensorMap tmap_a, const __grid
           if (lane == 0) ptx::mbar_arrive(box_bar(c >> 2));
         }
       }
-      if (sk_later) {
-        // publish this part: the barrier orders every epilogue thread's stores before thread
-        // 64's fence, and the fence (cumulative) orders them before the flag for whoever reads
-        // the flag and fences in turn.  One fence per CTA: a fence per thread waits for the
-        // thread's own stores under a saturated memory system, 256 times over.
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
-        if (threadIdx.x == 64 && ok) {
-          __threadfence();
-          *reinterpret_cast<volatile uint32_t*>(p.sk_flags + (static_cast<int64_t>(w.slot) * CG + cta_rank)) = 1u;
-        }
-      }
+      }   // pass
+      if (sk_later) publish_part(w.slot);
       // accumulator drained: hand the TMEM buffer back to the (leader's) MMA thread
       ptx::tc_fence_before_sync();
       __syncwarp();

@@ -119,11 +119,18 @@ __host__ __device__ inline void tile_coords(int32_t t, int32_t tiles_m, int32_t 
 //           `after` later parts, which other units left in workspace slots slot .. slot+after-1
 //   kind 2  a later part of a K-split tile: the raw accumulator goes to workspace slot `slot`
 //   kind 3  a split-K slice (every CTA has exactly one; folded by splitk_finish_kernel)
+//   kind 4  one of the two K halves of an exchanged tile: the unit stores the raw accumulator of
+//           the columns it does not finish to workspace slot `slot`, then adds the partner's
+//           part from slot `after` to the half of the columns it does finish (the left half of
+//           the tile when kb0 == 0, the right half otherwise) and runs the epilogue on it
 //
 // K-split last wave (GemmParams::stream_k): T tiles on U units leave R = T % U tiles for the last
 // wave; the whole waves before it are walked as usual.
 //   R <= U / 2  every last-wave tile is cut into S = U / R equal K slices, one per unit; the unit
-//               with slice 0 finishes the tile (slot of a later slice = its unit index).
+//               with slice 0 finishes the tile (slot of a later slice = its unit index).  With
+//               S = 2 and no fused reduction the two units exchange halves instead (kind 4): each
+//               publishes and each finishes half a tile, so neither the pass through the
+//               workspace nor the epilogue of a whole tile is left to one of them.
 //   R >  U / 2  owner units 0..R-1 take K blocks [0, num_kb - L) of their tile, where
 //               L = 3/4 num_kb (U - R) / U; the R L blocks left over form one stream in tile order that
 //               the U - R helper units share in equal contiguous runs.  A run crosses tile
@@ -178,6 +185,11 @@ struct WorkWalk {
           sk_kind = (used == 1) ? 0 : (slice == 0 ? 1 : 2);
           sk_after = slice == 0 ? used - 1 : 0;
           sk_slot = slice == 0 ? unit + 1 : unit;
+          if (slices == 2 && used == 2 && p.red_kinds == 0) {
+            sk_kind = 4;
+            sk_slot = unit;
+            sk_after = unit ^ 1;       // units 2j and 2j + 1 share tile j of the last wave
+          }
         }
       }
     } else if (slices == 1 && rem < units) {

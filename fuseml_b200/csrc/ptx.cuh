@@ -113,6 +113,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Acquire load of a flag another CTA raises after a fence: what that CTA wrote before the fence
+// is visible to this thread's later loads, without this thread waiting for its own stores in
+// flight (as a fence after a plain load would).
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // ---- programmatic dependent launch ---------------------------------------------
 // A kernel launched with the programmatic-stream-serialization attribute may be scheduled while
 // the previous kernel of the stream is still running.  griddep_wait() blocks until that kernel

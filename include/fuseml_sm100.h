@@ -337,7 +337,10 @@ typedef struct {
   int32_t kb0, kb1;    /* K blocks [kb0, kb1) of the tile                                         */
   int32_t kind;        /* 0 whole tile; 1 first part, finishes the tile after adding `after`
                           parts from workspace slots slot..slot+after-1; 2 later part, stored to
-                          workspace slot `slot`; 3 split-K slice                                   */
+                          workspace slot `slot`; 3 split-K slice; 4 one K half of a tile two
+                          units exchange: stores the columns it does not finish to slot `slot`,
+                          adds the partner's part from slot `after` to its own half of the columns
+                          (left when kb0 == 0, right otherwise) and finishes that half           */
   int32_t after, slot;
   int32_t tile_m, tile_n; /* the tile's row and column in units of tiles (plan.group_m and
                              FUSEML_PLAN_GROUP_N decide how `tile` maps onto them)                */

@@ -234,14 +234,18 @@ def test_k_split_schedule_covers_every_k_block_once(native_lib, M, Nn, K, grid):
     sched = _schedule(native_lib, d, p)
     assert len(sched) == units
     cover = {t: [0] * num_kb for t in range(tiles)}
-    finishers, parts, load = {}, {}, []
+    finishers, parts, load, halves = {}, {}, [], {}
     for u, items in sched.items():
         load.append(sum(w.kb1 - w.kb0 for w in items))
         for w in items:
-            assert 0 <= w.tile < tiles and 0 <= w.kb0 < w.kb1 <= num_kb and w.kind in (0, 1, 2)
+            assert 0 <= w.tile < tiles and 0 <= w.kb0 < w.kb1 <= num_kb and w.kind in (0, 1, 2, 4)
             for kb in range(w.kb0, w.kb1):
                 cover[w.tile][kb] += 1
-            if w.kind == 2:
+            if w.kind == 4:
+                # two units exchange halves: each writes its own slot and reads the partner's
+                assert 0 <= w.slot < units and 0 <= w.after < units and w.slot != w.after
+                halves.setdefault(w.tile, []).append(w)
+            elif w.kind == 2:
                 assert 0 <= w.slot < units and w.slot not in parts
                 parts[w.slot] = w.tile
             else:
@@ -249,7 +253,11 @@ def test_k_split_schedule_covers_every_k_block_once(native_lib, M, Nn, K, grid):
                 finishers[w.tile] = w
                 assert (w.kind == 0) == (w.after == 0) and (w.kind == 0) <= (w.kb1 - w.kb0 == num_kb)
     assert all(c == [1] * num_kb for c in cover.values())
-    assert sorted(finishers) == list(range(tiles))
+    for t, (a, b) in halves.items():
+        assert t not in finishers and {a.kb0, b.kb0} == {0, a.kb1 if a.kb0 == 0 else b.kb1}    # left finisher, right finisher
+        assert (a.slot, a.after) == (b.after, b.slot) and a.slot not in parts and b.slot not in parts
+    assert all(len(v) == 2 for v in halves.values())
+    assert sorted(list(finishers) + list(halves)) == list(range(tiles))
     read = {}
     for t, w in finishers.items():
         for s in range(w.slot, w.slot + w.after):
@@ -301,6 +309,23 @@ def test_rasterisation_visits_every_tile_position_once(native_lib, M, Nn, band, 
     inner = [c for _, c in first] if band else [r for r, _ in first]
     width = min(group, cols if band else rows)
     assert inner[:width] == list(range(width))        # the grouped index runs fastest
+
+
+def test_two_slice_tiles_are_exchanged_unless_a_reduction_is_fused(native_lib):
+    """Two K slices per last-wave tile: the two units exchange halves (kind 4) so that each
+    publishes and finishes half a tile; with a fused reduction (whose partials are laid out per
+    finishing warp) the first unit finishes the whole tile as with any other slice count."""
+    d = _desc(4096, 4096, 16384)
+    rc, p = _plan(native_lib, d)
+    assert rc == N.OK and p.flags & N.PLAN_STREAM_K
+    kinds = sorted({w.kind for items in _schedule(native_lib, d, p).values() for w in items})
+    assert kinds == [0, 4]
+    d.reduce.kinds = N.RED_SUM
+    d.reduce.axis = N.AXIS_N
+    d.reduce.out_sum = 0x40000
+    p.flags |= N.PLAN_STREAM_K
+    kinds = sorted({w.kind for items in _schedule(native_lib, d, p).values() for w in items})
+    assert kinds == [0, 1, 2]
 
 
 def test_saved_register_programs_keep_whole_tiles(native_lib):
